@@ -533,6 +533,50 @@ int pgk_seq_attention_ex(const float* q, int ldq, int q_off, const float* gate_r
                          const float* slopes, const float* sinks, int heads, int kv_heads, int dim, int vdim, int chunk,
                          int window, float scale, float softcap, int splits, float* workspace, uint32_t* tickets,
                          int single_query, void* stream);
+/* pgk_seq_attention_ex with three more optional parts.  slopes2 [heads] (with slopes): the distance term taken off the
+ * score is slopes[h] * ln(1 + slopes2[h] * (i - j)) instead of slopes[h] * (i - j).  keep_first > 0 (needs a window, no
+ * chunks): positions below keep_first stay visible from every later query, whatever the window.  weight_mode 1: the weight
+ * of a visible key is sigmoid(score + weight_bias[h]) (weight_bias [heads] or NULL) and the weights are not normalised over
+ * the keys (no sinks then); 0: softmax.  out_mult: a constant factor on the output. */
+int pgk_seq_attention_ex2(const float* q, int ldq, int q_off, const float* gate_rows, int ldg, int gate_off, int gate_mode,
+                          float* out, int ldo, const void* k_cache, const void* v_cache, int k_ld, int v_ld, int cache_dtype,
+                          const int32_t* table, int max_pages, int page_size, const int32_t* tiles, int n_tiles,
+                          const float* slopes, const float* slopes2, const float* sinks, int heads, int kv_heads, int dim,
+                          int vdim, int chunk, int window, int keep_first, float scale, float softcap, int weight_mode,
+                          const float* weight_bias, float out_mult, int splits, float* workspace, uint32_t* tickets,
+                          int single_query, void* stream);
+/* mixer_prep for layers with rotary positions in the half layout and a per-head norm after it: per token, on proj rows
+ * [.. q (q_off) .. k (k_off) .. v (v_off) ..], the first rot_dims elements of every query and key head are rotated by the
+ * token's position (element i paired with i + rot_dims / 2, angle = position * inv_freq[i], inv_freq [rot_dims / 2] doubles
+ * on the device; rot_dims 0: none); norm_mode 1 divides every head by its root mean square (eps inside the root), 2 also
+ * multiplies by q_weight / k_weight [dim], 0 leaves it; queries in place, keys and values (as projected) into the pages. */
+int pgk_seq_mixer_prep_rot(float* proj, int ld, int tokens, int heads, int kv_heads, int dim, int vdim, int q_off, int k_off,
+                           int v_off, int rot_dims, const double* inv_freq, int norm_mode, const float* q_weight,
+                           const float* k_weight, float eps, void* k_cache, void* v_cache, int cache_dtype, const int32_t* table,
+                           int max_pages, int page_size, const int32_t* slot, const int32_t* pos, void* stream);
+/* Per-sequence state instead of cache pages (seq_recurrent.cu); seqs [n_seqs][4] = (first row, rows, slot, first position)
+ * of every sequence of the step, rows of a sequence being consecutive.
+ * causal_conv_rows: u[t] = h[t] + sum_j weight[:, j] * h at position (pos[t] - taps + 1 + j), weight [width][taps]; inputs of
+ * earlier steps come from state [slots][taps - 1][width] (position p in ring row p mod (taps - 1)), positions below 0 are
+ * zero.  causal_conv_state: the step's last taps - 1 input rows of every sequence enter the ring (launch it after the rows).
+ * linear_prep, on proj rows holding q / k (heads x dim) and v (heads x vdim) at the three offsets: activation 1 = SiLU on
+ * all three; the first rot_dims elements of every q and k head rotated as in pgk_seq_mixer_prep_rot; k times k_scale.
+ * linear_attention: per head S <- decay[h] S + k v^T, out[t, h] = S^T q, token by token; state [slots][heads][dim][vdim]
+ * float32, taken as zero for a sequence whose first position is 0; value_slice = value columns per block
+ * (pgk_seq_linear_value_slice picks it from the grid it gives).
+ * linear_finish, in place on out rows: per_head 0: divided by the root mean square over heads x vdim, 1: head by head; times
+ * weight [heads x vdim] when given; times sigmoid (gate_act 1) or silu (2) of gate_rows[t, gate_off + i]; times mult. */
+int pgk_causal_conv_rows_f32(const float* h, float* u, const float* weight, float* state, const int32_t* slot,
+                             const int32_t* pos, int rows, int width, int taps, void* stream);
+int pgk_causal_conv_state_f32(const float* h, float* state, const int32_t* seqs, int n_seqs, int width, int taps, void* stream);
+int pgk_seq_linear_prep(float* proj, int ld, int tokens, int heads, int dim, int vdim, int q_off, int k_off, int v_off,
+                        int activation, int rot_dims, const double* inv_freq, float k_scale, const int32_t* pos, void* stream);
+int pgk_seq_linear_value_slice(int heads, int dim, int vdim, int n_seqs);
+int pgk_seq_linear_attention(const float* proj, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
+                             const float* decay, const int32_t* seqs, int n_seqs, int heads, int dim, int vdim, int value_slice,
+                             void* stream);
+int pgk_seq_linear_finish(float* o, int ldo, const float* gate_rows, int ldg, int gate_off, const float* weight, int tokens,
+                          int heads, int vdim, int per_head, int gate_act, float eps, float mult, void* stream);
 /* mixer_prep for layers whose q / k norm runs over the WHOLE projection: per token, q <- (q + q_bias) / rms(all heads x dim
  * of q) * (weight_offset + q_weight) in place (proj[t, 0 ..]), k the same from proj[t, k_off ..] with k_weight into the K
  * pages; the V pages receive k + k_bias as projected (before the norm).  Biases may be NULL; weights are [heads x dim] and
@@ -567,6 +611,7 @@ int pgk_embed_norm_rows_f32(const void* table, int wdt, const int32_t* tokens, c
 /* The general row GEMM: `batch` products over the same M rows, product b reading A columns from b * a_batch, matrix
  * W + b * w_batch and writing C columns from b * c_batch (one product per attention head).  Epilogues 0-2 as above with
  * p0 = scale, p1 = cap; 3: gate/up pairs, g = min(gate, p1), u = clamp(up, -p1, p1), C[m, j] = g sigmoid(p0 g) (u + 1);
+ * 6: C[m, n] = max(product, 0)^2;
  * 4: C[m, n] += col_scale[n] * product; 5: C[m, n] = gelu_tanh(product) * aux[aux_rows[m], aux_off + n] (aux float32 = 0 or
  * bfloat16 = 2, row stride aux_ld).  rows_per_block > 0: the few-row kernel (M rows in blocks of at most 8), 0: tiles. */
 int pgk_gemm_seq_f32(const float* A, int lda, long long a_batch, const void* W, int wdt, long long w_batch, float* C, int ldc,

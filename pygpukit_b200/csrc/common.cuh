@@ -249,6 +249,15 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
         :: "r"(smem_u32(bar)), "r"(parity) : "memory");
 }
 
+// sine and cosine of position * inv_freq: the angle is formed and reduced to [-pi, pi] in double (at positions in the
+// thousands a float32 product has lost four digits), the functions themselves are float32
+__device__ __forceinline__ void rope_angle_sincos(int pos, double inv_freq, float& sn, float& cs) {
+    const double a = (double)pos * inv_freq;
+    const double two_pi = 6.283185307179586476925286766559;
+    const float r = (float)(a - two_pi * rint(a / two_pi));
+    sincosf(r, &sn, &cs);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -75,6 +75,60 @@ __global__ void __launch_bounds__(128) mixer_prep_kernel(PrepArgs a) {
     }
 }
 
+struct PrepRotArgs {
+    float* proj; int ld;
+    int H, G, D, Dv, q_off, k_off, v_off;
+    int rot_dims; const double* inv_freq;
+    int norm;                                        // 0: none, 1: divide by the root mean square, 2: and multiply by qw / kw
+    const float* qw; const float* kw; float eps;
+    void* kc; void* vc; const int* table; int max_pages, PS;
+    const int* slot; const int* pos;
+};
+
+// units: H query heads (rotated and normalised in place), G key heads and G value heads (into the cache); a warp each.
+// Rotation: element i < rot_dims / 2 of a head is paired with element i + rot_dims / 2, angle = position * inv_freq[i].
+template <typename TC>
+__global__ void __launch_bounds__(128) mixer_prep_rot_kernel(PrepRotArgs a) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int u = blockIdx.y * 4 + warp;
+    if (u >= a.H + 2 * a.G) return;
+    float* row = a.proj + (size_t)t * a.ld;
+    const int pos = a.pos[t], slot = a.slot[t];
+    const int page = a.table[(size_t)slot * a.max_pages + pos / a.PS], r = pos % a.PS;
+    if (u >= a.H + a.G) {
+        const int g = u - a.H - a.G;
+        const float* v = row + a.v_off + (size_t)g * a.Dv;
+        TC* dst = (TC*)a.vc + (((size_t)page * a.G + g) * a.PS + r) * a.Dv;
+        for (int d = lane; d < a.Dv; d += 32) cstore<TC>(dst + d, v[d]);
+        return;
+    }
+    const bool is_k = u >= a.H;
+    const int g = u - a.H;
+    float* x = row + (is_k ? a.k_off + (size_t)g * a.D : a.q_off + (size_t)u * a.D);
+    if (!is_k && a.rot_dims == 0 && a.norm == 0) return;           // the query stays as projected
+    const int half = a.rot_dims / 2;
+    float ss = 0.f;
+    for (int i = lane; i < half; i += 32) {
+        float sn, cs;
+        rope_angle_sincos(pos, a.inv_freq[i], sn, cs);
+        const float p0 = x[i], p1 = x[i + half];
+        const float r0 = p0 * cs - p1 * sn, r1 = p1 * cs + p0 * sn;
+        x[i] = r0; x[i + half] = r1;
+        ss = fmaf(r0, r0, fmaf(r1, r1, ss));
+    }
+    for (int d = 2 * half + lane; d < a.D; d += 32) ss = fmaf(x[d], x[d], ss);
+    __syncwarp();
+    float inv = 1.f;
+    if (a.norm) inv = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
+    const float* w = a.norm == 2 ? (is_k ? a.kw : a.qw) : nullptr;
+    if (is_k) {
+        TC* dst = (TC*)a.kc + (((size_t)page * a.G + g) * a.PS + r) * a.D;
+        for (int d = lane; d < a.D; d += 32) cstore<TC>(dst + d, x[d] * inv * (w ? w[d] : 1.f));
+    } else if (a.norm) {
+        for (int d = lane; d < a.D; d += 32) x[d] = x[d] * inv * (w ? w[d] : 1.f);
+    }
+}
+
 struct PrepAllArgs {
     float* proj; int ld;
     int H, G, D, k_off;
@@ -141,6 +195,11 @@ struct AttnArgs {
     int valias;                         // the value rows are the first Dv elements of the key rows (one staging)
     const int4* tiles;                  // (first token row, queries, slot, first position)
     const float* slopes;                // [H] or NULL
+    const float* slopes2;               // [H] or NULL: the distance term is slopes[h] * ln(1 + slopes2[h] * (i - j)) instead
+    int keep;                           // with a window: the first `keep` positions stay visible beyond it
+    int prob;                           // 0: softmax over the visible keys; 1: weight sigmoid(score + pbias[h]), not normalised
+    const float* pbias;                 // [H] or NULL
+    float out_mult;                     // constant factor on the output
     int H, G, D, Dv, chunk, HB, gate;
     float scale, cap;
     int splits; float* ws;              // splits > 1: partial (m, l, acc[Dv]) records [row][H][splits][Dv + 2]
@@ -156,6 +215,13 @@ __device__ __forceinline__ int first_key(const AttnArgs& a, int pos) {
     int lo = a.chunk > 0 ? (pos / a.chunk) * a.chunk : 0;
     if (a.window > 0) lo = max(lo, pos - a.window + 1);
     return lo;
+}
+// The keys of a tile whose lowest window start is jlo come in two runs: the kept first positions below jlo, [0, kept), and
+// [jlo, jhi].  Key tile ti covers KT positions from tile_first(); positions past tile_last() are padding.
+__device__ __forceinline__ int kept_below(const AttnArgs& a, int jlo) { return a.window > 0 ? min(a.keep, jlo) : 0; }
+__device__ __forceinline__ float distance_term(float slope, float slope2, bool log_form, int dist) {
+    const float d = (float)max(dist, 0);
+    return log_form ? slope * log1pf(slope2 * d) : slope * d;
 }
 
 // KT cache rows of n elements -> shared memory as float32 (row stride ld), 16 bytes per load when the rows allow it;
@@ -211,7 +277,8 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
     // this warp's pairs
     int qi[PPW], hd[PPW], pi[PPW], lo[PPW];
     bool ok[PPW];
-    float slope[PPW];
+    float slope[PPW], slope2[PPW], pb[PPW];
+    const bool log_form = a.slopes2 != nullptr;
 #pragma unroll
     for (int c = 0; c < PPW; ++c) {
         const int p = warp * PPW + c;
@@ -222,6 +289,8 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
         pi[c] = pos0 + qi[c];
         lo[c] = first_key(a, pi[c]);
         slope[c] = (ok[c] && a.slopes) ? a.slopes[hd[c]] : 0.f;
+        slope2[c] = (ok[c] && a.slopes2) ? a.slopes2[hd[c]] : 0.f;
+        pb[c] = (ok[c] && a.pbias) ? a.pbias[hd[c]] : 0.f;
     }
     const bool warp_live = ok[0] || ok[1] || ok[2] || ok[3];
     for (int i = lane; i < D * PPW; i += 32) {
@@ -237,6 +306,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
     for (int c = 0; c < PPW; ++c) {
         m[c] = -INFINITY; l[c] = 0.f;
         if (a.sinks && ok[c] && blockIdx.z == 0) { m[c] = a.sinks[hd[c]]; l[c] = 1.f; }    // the sink counts once: slice 0
+        if (a.prob) { m[c] = 0.f; l[c] = blockIdx.z == 0 ? 1.f : 0.f; }                    // plain sums: the slices' weights are 1
 #pragma unroll
         for (int v = 0; v < NV; ++v) acc[c][v] = 0.f;
     }
@@ -244,15 +314,17 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
     const TC* kc = (const TC*)a.kc;
     const TC* vc = (const TC*)a.vc;
     // this block's slice of the key tiles (all of them when splits == 1)
-    const int ntile = (jhi - jlo) / KT + 1, per = (ntile + a.splits - 1) / a.splits;
-    const int jbeg = jlo + (int)blockIdx.z * per * KT;
-    const int jend = min(jhi, jbeg + per * KT - 1);
-    for (int j0 = jbeg; j0 <= jend; j0 += KT) {
+    const int kept = kept_below(a, jlo), nkept = (kept + KT - 1) / KT;
+    const int ntile = nkept + (jhi - jlo) / KT + 1, per = (ntile + a.splits - 1) / a.splits;
+    const int tbeg = (int)blockIdx.z * per, tend = min(ntile, tbeg + per);
+    for (int ti = tbeg; ti < tend; ++ti) {
+        const int j0 = ti < nkept ? ti * KT : jlo + (ti - nkept) * KT;
+        const int jmax = ti < nkept ? kept - 1 : jhi;
         __syncthreads();
         if (threadIdx.x < KT) {
             const int j = j0 + threadIdx.x;
             long long ko = -1, vo = -1;
-            if (j <= jhi) {
+            if (j <= jmax) {
                 const int page = a.table[(size_t)slot * a.max_pages + j / a.PS], r = j % a.PS;
                 ko = (((long long)page * a.G + g) * a.PS + r) * a.kld;
                 vo = (((long long)page * a.G + g) * a.PS + r) * a.vld;
@@ -280,8 +352,9 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
         for (int c = 0; c < PPW; ++c) {
             float sc = s[c] * a.scale;
             if (a.cap > 0.f) sc = a.cap * tanhf(sc / a.cap);
-            sc -= slope[c] * (float)(pi[c] - j);
-            const bool vis = ok[c] && j <= pi[c] && j >= lo[c];
+            sc -= distance_term(slope[c], slope2[c], log_form, pi[c] - j);
+            const bool vis = ok[c] && j <= jmax && j <= pi[c] && (j >= lo[c] || j < a.keep);
+            if (a.prob) { p[c] = vis ? 1.f / (1.f + expf(-(sc + pb[c]))) : 0.f; continue; }
             sc = vis ? sc : -INFINITY;
             const float mn = fmaxf(m[c], warp_max(sc));
             if (mn == -INFINITY) { p[c] = 0.f; continue; }      // uniform across the warp
@@ -292,7 +365,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
 #pragma unroll
             for (int v = 0; v < NV; ++v) acc[c][v] *= corr;
         }
-        const int nvalid = min(KT, jhi - j0 + 1);
+        const int nvalid = min(KT, jmax - j0 + 1);
         for (int jj = 0; jj < nvalid; ++jj) {
             float pj[PPW];
 #pragma unroll
@@ -366,7 +439,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
 #pragma unroll 8
             for (int sp = 0; sp < a.splits; ++sp) o = fmaf(wsl[p][sp], __ldcg(rec + (size_t)sp * (Dv + 2)), o);
             if (a.gate) o *= 1.f / (1.f + expf(-gate_logit(a, t, h, dv)));
-            a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
+            a.out[t * a.ldo + (size_t)h * Dv + dv] = o * a.out_mult;
         }
         return;
     }
@@ -381,7 +454,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
             if (dv >= Dv) continue;
             float o = acc[c][v] * inv;
             if (a.gate) o *= 1.f / (1.f + expf(-gate_logit(a, t, hd[c], dv)));
-            a.out[t * a.ldo + (size_t)hd[c] * Dv + dv] = o;
+            a.out[t * a.ldo + (size_t)hd[c] * Dv + dv] = o * a.out_mult;
         }
     }
 }
@@ -491,17 +564,24 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
         const int p = i / D, d = i - p * D;
         qs[i] = p < nh ? a.proj[(size_t)t0 * a.ld + a.q_off + (size_t)(hb0 + p) * D + d] : 0.f;
     }
-    float slope[DPAIRS];
+    float slope[DPAIRS], slope2[DPAIRS], pb[DPAIRS];
+    const bool log_form = a.slopes2 != nullptr;
 #pragma unroll
-    for (int p = 0; p < DPAIRS; ++p) slope[p] = (p < nh && a.slopes) ? a.slopes[hb0 + p] : 0.f;
+    for (int p = 0; p < DPAIRS; ++p) {
+        slope[p] = (p < nh && a.slopes) ? a.slopes[hb0 + p] : 0.f;
+        slope2[p] = (p < nh && a.slopes2) ? a.slopes2[hb0 + p] : 0.f;
+        pb[p] = (p < nh && a.pbias) ? a.pbias[hb0 + p] : 0.f;
+    }
     // ... and the page of the warp's first key tile
     const int jlo = first_key(a, pos), jhi = pos;
-    const int ntile = (jhi - jlo) / KT + 1, per = (ntile + a.splits - 1) / a.splits;
+    const int kept = kept_below(a, jlo), nkept = (kept + KT - 1) / KT;
+    const int ntile = nkept + (jhi - jlo) / KT + 1, per = (ntile + a.splits - 1) / a.splits;
     const int tb = (int)blockIdx.z * per, te = min(ntile, tb + per);
     int page_first = 0;
     {
-        const int j = jlo + (tb + warp) * KT + lane;
-        if (tb + warp < te && j <= jhi) page_first = a.table[(size_t)slot * a.max_pages + j / a.PS];
+        const int ti = tb + warp;
+        const int j = (ti < nkept ? ti * KT : jlo + (ti - nkept) * KT) + lane;
+        if (ti < te && j <= (ti < nkept ? kept - 1 : jhi)) page_first = a.table[(size_t)slot * a.max_pages + j / a.PS];
     }
     __syncthreads();
 
@@ -510,6 +590,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
     for (int p = 0; p < DPAIRS; ++p) {
         m[p] = -INFINITY; l[p] = 0.f;
         if (a.sinks && p < nh && warp == 0 && blockIdx.z == 0) { m[p] = a.sinks[hb0 + p]; l[p] = 1.f; }   // counted once
+        if (a.prob) { m[p] = 0.f; l[p] = (warp == 0 && blockIdx.z == 0) ? 1.f : 0.f; }                   // plain sums
 #pragma unroll
         for (int v = 0; v < NV; ++v) acc[p][v] = 0.f;
     }
@@ -520,8 +601,9 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
     const bool kvec = D % KV == 0 && a.kld % KV == 0;
     const bool vvec = Dv % NV == 0 && a.vld % NV == 0 && (NV * (int)sizeof(TC) <= 16 || a.vld % KV == 0);
     for (int ti = tb + warp; ti < te; ti += NWARP) {
-        const int j = jlo + ti * KT + lane;
-        const bool in = j <= jhi;
+        const int j0 = ti < nkept ? ti * KT : jlo + (ti - nkept) * KT, jmax = ti < nkept ? kept - 1 : jhi;
+        const int j = j0 + lane;
+        const bool in = j <= jmax;
         long long ko = 0, vo = 0;
         if (in) {
             const int page = ti == tb + warp ? page_first : a.table[(size_t)slot * a.max_pages + j / a.PS], r = j % a.PS;
@@ -573,7 +655,8 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
         for (int p = 0; p < DPAIRS; ++p) {
             float sc = s[p] * a.scale;
             if (a.cap > 0.f) sc = a.cap * tanhf(sc / a.cap);
-            sc -= slope[p] * (float)(pos - j);
+            sc -= distance_term(slope[p], slope2[p], log_form, pos - j);
+            if (a.prob) { pr[p] = (in && p < nh) ? 1.f / (1.f + expf(-(sc + pb[p]))) : 0.f; continue; }
             sc = (in && p < nh) ? sc : -INFINITY;
             const float mn = fmaxf(m[p], warp_max(sc));
             if (mn == -INFINITY) { pr[p] = 0.f; continue; }
@@ -584,7 +667,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
 #pragma unroll
             for (int v = 0; v < NV; ++v) acc[p][v] *= corr;
         }
-        const int nvalid = min(KT, jhi - (jlo + ti * KT) + 1);
+        const int nvalid = min(KT, jmax - j0 + 1);
         const int dv0 = lane * NV;
         for (int jj0 = 0; jj0 < nvalid; jj0 += VR) {               // VR value rows in flight
             float vv[VR][NV];
@@ -649,7 +732,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
                 if (u >= GPT) z = gate_logit(a, t, h, dv);
                 o *= 1.f / (1.f + expf(-z));
             }
-            a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
+            a.out[t * a.ldo + (size_t)h * Dv + dv] = o * a.out_mult;
         }
     }
     if (a.splits == 1) return;
@@ -702,7 +785,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
             if (u >= GPT) z = gate_logit(a, t, h, dv);
             o *= 1.f / (1.f + expf(-z));
         }
-        a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
+        a.out[t * a.ldo + (size_t)h * Dv + dv] = o * a.out_mult;
     }
 }
 
@@ -774,6 +857,23 @@ int pgk_seq_attention_ex(const float* q, int ldq, int q_off, const float* gate_r
                          const float* slopes, const float* sinks, int heads, int kv_heads, int dim, int vdim, int chunk,
                          int window, float scale, float softcap, int splits, float* workspace, uint32_t* tickets,
                          int single_query, void* stream) {
+    return pgk_seq_attention_ex2(q, ldq, q_off, gate_rows, ldg, gate_off, gate_mode, out, ldo, k_cache, v_cache, k_ld, v_ld,
+                                 cache_dtype, table, max_pages, page_size, tiles, n_tiles, slopes, nullptr, sinks, heads,
+                                 kv_heads, dim, vdim, chunk, window, 0, scale, softcap, 0, nullptr, 1.f, splits, workspace, tickets,
+                                 single_query, stream);
+}
+
+int pgk_seq_attention_ex2(const float* q, int ldq, int q_off, const float* gate_rows, int ldg, int gate_off, int gate_mode,
+                          float* out, int ldo, const void* k_cache, const void* v_cache, int k_ld, int v_ld, int cache_dtype,
+                          const int32_t* table, int max_pages, int page_size, const int32_t* tiles, int n_tiles,
+                          const float* slopes, const float* slopes2, const float* sinks, int heads, int kv_heads, int dim,
+                          int vdim, int chunk, int window, int keep_first, float scale, float softcap, int weight_mode,
+                          const float* weight_bias, float out_mult, int splits, float* workspace, uint32_t* tickets,
+                          int single_query, void* stream) {
+    PGK_REQUIRE(keep_first >= 0 && (keep_first == 0 || (window > 0 && chunk == 0)),
+                "seq_attention failed: kept first positions need a window and no chunks");
+    PGK_REQUIRE(!slopes2 || slopes, "seq_attention failed: the logarithmic distance term needs both per-head vectors");
+    PGK_REQUIRE(weight_mode == 0 || (weight_mode == 1 && !sinks), "seq_attention failed: weight mode %d", weight_mode);
     PGK_REQUIRE(cache_dtype == 0 || cache_dtype == 2, "seq_attention failed: the cache is float32 (0) or bfloat16 (2), got %d", cache_dtype);
     PGK_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "seq_attention failed: invalid head layout");
     PGK_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (workspace && tickets)),
@@ -787,7 +887,8 @@ int pgk_seq_attention_ex(const float* q, int ldq, int q_off, const float* gate_r
     a.kc = k_cache; a.vc = v_cache; a.table = table; a.max_pages = max_pages; a.PS = page_size;
     a.gsrc = gate_rows; a.ldg = ldg; a.sinks = sinks; a.window = window; a.kld = k_ld; a.vld = v_ld;
     a.valias = (k_cache == v_cache && k_ld == v_ld && vdim <= dim) ? 1 : 0;
-    a.tiles = (const int4*)tiles; a.slopes = slopes;
+    a.tiles = (const int4*)tiles; a.slopes = slopes; a.slopes2 = slopes2;
+    a.keep = window > 0 ? keep_first : 0; a.prob = weight_mode; a.pbias = weight_bias; a.out_mult = out_mult;
     a.H = heads; a.G = kv_heads; a.D = dim; a.Dv = vdim; a.chunk = chunk;
     a.HB = pgk_seq_heads_per_block(heads, kv_heads); a.gate = gate_mode;
     a.scale = scale; a.cap = softcap; a.splits = splits; a.ws = workspace; a.tickets = tickets;
@@ -823,5 +924,24 @@ int pgk_seq_mixer_prep_all(float* proj, int ld, int tokens, int heads, int kv_he
     return 0;
 }
 int pgk_seq_decode_heads_per_block(void) { return DPAIRS_MAX; }
+
+// ---- rotary positions (half layout) and a per-head norm with or without weights, K / V rows into the cache
+int pgk_seq_mixer_prep_rot(float* proj, int ld, int tokens, int heads, int kv_heads, int dim, int vdim, int q_off, int k_off,
+                           int v_off, int rot_dims, const double* inv_freq, int norm_mode, const float* q_weight,
+                           const float* k_weight, float eps, void* k_cache, void* v_cache, int cache_dtype, const int32_t* table,
+                           int max_pages, int page_size, const int32_t* slot, const int32_t* pos, void* stream) {
+    PGK_REQUIRE(cache_dtype == 0 || cache_dtype == 2, "seq_mixer_prep_rot failed: the cache is float32 (0) or bfloat16 (2), got %d", cache_dtype);
+    PGK_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "seq_mixer_prep_rot failed: invalid head layout");
+    PGK_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || inv_freq),
+                "seq_mixer_prep_rot failed: %d rotated dimensions in heads of %d", rot_dims, dim);
+    PGK_REQUIRE(norm_mode >= 0 && norm_mode <= 2 && (norm_mode != 2 || (q_weight && k_weight)), "seq_mixer_prep_rot failed: norm mode %d", norm_mode);
+    if (tokens <= 0) return 0;
+    PrepRotArgs a{proj, ld, heads, kv_heads, dim, vdim, q_off, k_off, v_off, rot_dims, inv_freq, norm_mode, q_weight, k_weight, eps,
+                  k_cache, v_cache, table, max_pages, page_size, slot, pos};
+    const dim3 grid(tokens, (heads + 2 * kv_heads + 3) / 4);
+    if (cache_dtype == 2) PGK_CUDA(launch(mixer_prep_rot_kernel<uint16_t>, grid, dim3(128), 0, (cudaStream_t)stream, a));
+    else PGK_CUDA(launch(mixer_prep_rot_kernel<float>, grid, dim3(128), 0, (cudaStream_t)stream, a));
+    return 0;
+}
 
 }  // extern "C"

@@ -66,6 +66,10 @@ __device__ __forceinline__ void store_pair(const GemmArgs& a, int row, int col, 
         c0 *= a.scale; c1 *= a.scale;
         if (a.cap > 0.f) { c0 = a.cap * tanhf(c0 / a.cap); c1 = a.cap * tanhf(c1 / a.cap); }
     }
+    if (EPI == 6) {          // squared ReLU
+        c0 = fmaxf(c0, 0.f); c1 = fmaxf(c1, 0.f);
+        c0 *= c0; c1 *= c1;
+    }
     float* p = a.C + (size_t)row * a.ldc + col;
     if (EPI == 4) {
         if (col < a.N) p[0] = fmaf(a.colv[col], c0, p[0]);
@@ -477,7 +481,7 @@ int pgk_gemm_seq_f32(const float* A, int lda, long long a_batch, const void* W, 
                      void* stream) {
     PGK_REQUIRE(wdt == 0 || wdt == 2, "gemm_seq_f32 failed: weights must be float32 (0) or bfloat16 (2), got %d", wdt);
     PGK_REQUIRE(N > 0 && K > 0 && M >= 0 && batch >= 1, "gemm_seq_f32 failed: invalid shape M=%d N=%d K=%d batch=%d", M, N, K, batch);
-    PGK_REQUIRE(epilogue >= 0 && epilogue <= 5, "gemm_seq_f32 failed: unknown epilogue %d", epilogue);
+    PGK_REQUIRE(epilogue >= 0 && epilogue <= 6, "gemm_seq_f32 failed: unknown epilogue %d", epilogue);
     PGK_REQUIRE((epilogue != 1 && epilogue != 3) || N % 2 == 0, "gemm_seq_f32 failed: a gate/up epilogue needs an even N");
     PGK_REQUIRE(epilogue != 4 || col_scale, "gemm_seq_f32 failed: the scaled-accumulate epilogue needs its column factors");
     PGK_REQUIRE(epilogue != 5 || (aux && aux_rows && (aux_dtype == 0 || aux_dtype == 2)), "gemm_seq_f32 failed: the gather epilogue needs its table and rows");
@@ -493,7 +497,8 @@ int pgk_gemm_seq_f32(const float* A, int lda, long long a_batch, const void* W, 
             case 2: return launch_few<2>(a, wdt, rows_per_block, st, batch);
             case 3: return launch_few<3>(a, wdt, rows_per_block, st, batch);
             case 4: return launch_few<4>(a, wdt, rows_per_block, st, batch);
-            default: return launch_few<5>(a, wdt, rows_per_block, st, batch);
+            case 5: return launch_few<5>(a, wdt, rows_per_block, st, batch);
+            default: return launch_few<6>(a, wdt, rows_per_block, st, batch);
         }
     }
     switch (epilogue) {
@@ -502,7 +507,8 @@ int pgk_gemm_seq_f32(const float* A, int lda, long long a_batch, const void* W, 
         case 2: return launch_many<2>(a, wdt, batch, M, st);
         case 3: return launch_many<3>(a, wdt, batch, M, st);
         case 4: return launch_many<4>(a, wdt, batch, M, st);
-        default: return launch_many<5>(a, wdt, batch, M, st);
+        case 5: return launch_many<5>(a, wdt, batch, M, st);
+        default: return launch_many<6>(a, wdt, batch, M, st);
     }
 }
 

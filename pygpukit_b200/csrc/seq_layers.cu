@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(256) combine_norm_kernel(NormArgs a) {
     const float var = block_sum256(q, red) / (float)a.W;
     const float inv = 1.f / sqrtf(var + a.eps);
     for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
-        const float v = (y[i] - mean) * inv * a.gamma[i] + a.beta[i];
+        const float v = (y[i] - mean) * inv * a.gamma[i] + (a.beta ? a.beta[i] : 0.f);
         float* o = a.out + (size_t)t * a.W + i;
         *o = a.add ? *o + v : v;
     }

@@ -1,0 +1,297 @@
+// seq_recurrent.cu -- the parts of the token-major models that carry per-sequence STATE instead of cache pages, all in
+// float32: a short causal convolution over time in front of a sublayer, and linear attention with a fixed decay per head.
+//
+//   causal_conv_rows   u_t = h_t + sum_j w[:, j] h_(t - taps + 1 + j), channel by channel.  Inputs of the same step come
+//                      from the rows before it (rows of a sequence are consecutive), older ones from the sequence's state:
+//                      a ring of taps - 1 rows per slot, position p at ring row p mod (taps - 1); positions below 0 are zero.
+//   causal_conv_state  the step's last taps - 1 inputs of every sequence enter the ring (a launch of its own: rows of the
+//                      same launch still read the old ring).
+//   linear_prep        per token and head on the fused projection row: activation of q / k / v, rotation of q and k (the
+//                      first rot_dims elements, element i paired with i + rot_dims / 2), k scaled.
+//   linear_attention   S_t = a_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t.  A block owns one (sequence, head, slice of value
+//                      columns): it keeps S [D][slice] in shared memory, walks the step's tokens in chunks of 32 --
+//                      scores q_t.k_s a^(t-s) inside the chunk, the carried state for everything before it -- and leaves
+//                      the state in the slot's array.  A sequence whose first position is 0 starts from zero, whatever the
+//                      slot held.  One decoded token is a chunk of one.
+//   linear_finish      the heads' outputs divided by their root mean square (over all heads with a weight, or head by head
+//                      without one), times sigmoid or silu of the gate columns, times a constant.
+#include "common.cuh"
+#include "../../include/pgk_b200.h"
+
+using namespace pgk;
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+
+// ---------------------------------------------------------------- causal convolution
+struct ConvArgs {
+    const float* h; float* u; const float* w; float* state;
+    const int* slot; const int* pos; int W, taps;
+};
+
+__global__ void __launch_bounds__(256) causal_conv_rows_kernel(ConvArgs a) {
+    const int t = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
+    if (c >= a.W) return;
+    const int p = a.pos[t], s = a.slot[t], ring = a.taps - 1;
+    const float* w = a.w + (size_t)c * a.taps;
+    const float hv = a.h[(size_t)t * a.W + c];
+    float acc = fmaf(w[a.taps - 1], hv, hv);
+    for (int k = 1; k < a.taps && k <= p; ++k) {
+        float v;
+        if (t - k >= 0 && a.slot[t - k] == s) v = a.h[(size_t)(t - k) * a.W + c];
+        else v = a.state[((size_t)s * ring + (p - k) % ring) * a.W + c];
+        acc = fmaf(w[a.taps - 1 - k], v, acc);
+    }
+    a.u[(size_t)t * a.W + c] = acc;
+}
+
+// seqs [n][4] = (first row, rows, slot, first position); block x = sequence * ring + i: the i-th last row of the sequence
+__global__ void __launch_bounds__(256) causal_conv_state_kernel(const float* h, float* state, const int4* seqs, int W, int ring) {
+    const int4 sq = seqs[blockIdx.x / ring];
+    const int i = blockIdx.x % ring, c = blockIdx.y * 256 + threadIdx.x;
+    if (i >= sq.y || c >= W) return;
+    const int r = sq.y - 1 - i, p = sq.w + r;
+    state[((size_t)sq.z * ring + p % ring) * W + c] = h[(size_t)(sq.x + r) * W + c];
+}
+
+// ---------------------------------------------------------------- linear attention: preparation of q / k / v
+struct LinPrepArgs {
+    float* proj; int ld, H, D, Dv, q_off, k_off, v_off, act, rot_dims;
+    const double* inv_freq; float k_scale; const int* pos;
+};
+
+// units per token: H query heads, H key heads, H value heads; a warp each
+__global__ void __launch_bounds__(128) linear_prep_kernel(LinPrepArgs a) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, u = blockIdx.y * 4 + (threadIdx.x >> 5);
+    if (u >= 3 * a.H) return;
+    float* row = a.proj + (size_t)t * a.ld;
+    if (u >= 2 * a.H) {
+        if (!a.act) return;
+        float* v = row + a.v_off + (size_t)(u - 2 * a.H) * a.Dv;
+        for (int d = lane; d < a.Dv; d += 32) v[d] = silu_f(v[d]);
+        return;
+    }
+    const bool is_k = u >= a.H;
+    float* x = row + (is_k ? a.k_off + (size_t)(u - a.H) * a.D : a.q_off + (size_t)u * a.D);
+    const float sc = is_k ? a.k_scale : 1.f;
+    const int half = a.rot_dims / 2, pos = a.pos[t];
+    for (int i = lane; i < half; i += 32) {
+        float p0 = x[i], p1 = x[i + half];
+        if (a.act) { p0 = silu_f(p0); p1 = silu_f(p1); }
+        float sn, cs;
+        rope_angle_sincos(pos, a.inv_freq[i], sn, cs);
+        x[i] = (p0 * cs - p1 * sn) * sc;
+        x[i + half] = (p1 * cs + p0 * sn) * sc;
+    }
+    for (int d = 2 * half + lane; d < a.D; d += 32) x[d] = (a.act ? silu_f(x[d]) : x[d]) * sc;
+}
+
+// ---------------------------------------------------------------- linear attention: the recurrence
+constexpr int LC = 32;                  // tokens per chunk
+
+struct LinArgs {
+    const float* proj; int ld, q_off, k_off, v_off;
+    float* out; int ldo;
+    float* state;                        // [slots][H][D][Dv]
+    const float* decay;                  // [H]
+    const int4* seqs;                    // (first row, rows, slot, first position)
+    int H, D, Dv, DS;                    // DS: value columns per block
+};
+
+__global__ void __launch_bounds__(256) linear_attention_kernel(LinArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int D = a.D, DS = a.DS, DP = D + 1;
+    float* S = sm;                      // [D][DS]
+    float* Q = S + D * DS;              // [LC][D + 1]
+    float* K = Q + LC * DP;             // [LC][D + 1]
+    float* V = K + LC * DP;             // [LC][DS]
+    float* A = V + LC * DS;             // [LC][LC + 1]
+    float* pw = A + LC * (LC + 1);      // [LC + 1]: decay^i
+    const int4 sq = a.seqs[blockIdx.x];
+    const int row0 = sq.x, n = sq.y, slot = sq.z, pos0 = sq.w;
+    const int h = blockIdx.y, dv0 = blockIdx.z * DS, nd = min(DS, a.Dv - dv0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float dec = a.decay[h];
+    float* Sg = a.state + (((size_t)slot * a.H + h) * D) * a.Dv + dv0;
+    for (int i = tid; i < D * DS; i += 256) {
+        const int d = i / DS, c = i - d * DS;
+        S[i] = (pos0 > 0 && c < nd) ? Sg[(size_t)d * a.Dv + c] : 0.f;
+    }
+    if (tid <= LC) pw[tid] = powf(dec, (float)tid);
+    for (int c0 = 0; c0 < n; c0 += LC) {
+        const int nc = min(LC, n - c0);
+        __syncthreads();
+        for (int i = tid; i < nc * D; i += 256) {
+            const int r = i / D, d = i - r * D;
+            const float* src = a.proj + (size_t)(row0 + c0 + r) * a.ld + (size_t)h * D + d;
+            Q[r * DP + d] = src[a.q_off];
+            K[r * DP + d] = src[a.k_off];
+        }
+        for (int i = tid; i < nc * DS; i += 256) {
+            const int r = i / DS, c = i - r * DS;
+            V[i] = c < nd ? a.proj[(size_t)(row0 + c0 + r) * a.ld + a.v_off + (size_t)h * a.Dv + dv0 + c] : 0.f;
+        }
+        __syncthreads();
+        // scores inside the chunk: lane = key s, the warp's rows t = warp, warp + 8, ...
+        for (int t = warp; t < nc; t += 8) {
+            float s = 0.f;
+            if (lane <= t) {
+                const float* q = Q + t * DP;
+                const float* k = K + lane * DP;
+                for (int d = 0; d < D; ++d) s = fmaf(q[d], k[d], s);
+                s *= pw[t - lane];
+            }
+            A[t * (LC + 1) + lane] = s;
+        }
+        __syncthreads();
+        // outputs: o_t = a^(t + 1) S^T q_t + sum_{s <= t} A[t][s] v_s
+        for (int i = tid; i < nc * DS; i += 256) {
+            const int t = i / DS, c = i - t * DS;
+            if (c >= nd) continue;
+            const float* q = Q + t * DP;
+            float o = 0.f;
+            for (int d = 0; d < D; ++d) o = fmaf(q[d], S[d * DS + c], o);
+            o *= pw[t + 1];
+            const float* ar = A + t * (LC + 1);
+            for (int s = 0; s <= t; ++s) o = fmaf(ar[s], V[s * DS + c], o);
+            a.out[(size_t)(row0 + c0 + t) * a.ldo + (size_t)h * a.Dv + dv0 + c] = o;
+        }
+        __syncthreads();
+        // state: S <- a^nc S + sum_s a^(nc - 1 - s) k_s v_s^T
+        for (int i = tid; i < D * DS; i += 256) {
+            const int d = i / DS, c = i - d * DS;
+            float sv = S[i] * pw[nc];
+            for (int s = 0; s < nc; ++s) sv = fmaf(K[s * DP + d] * pw[nc - 1 - s], V[s * DS + c], sv);
+            S[i] = sv;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < D * DS; i += 256) {
+        const int d = i / DS, c = i - d * DS;
+        if (c < nd) Sg[(size_t)d * a.Dv + c] = S[i];
+    }
+}
+
+// ---------------------------------------------------------------- linear attention: output norm and gate
+struct LinFinishArgs {
+    float* o; int ldo; const float* gate; int ldg, g_off;
+    const float* w;                      // [H * Dv] or NULL
+    int H, Dv, per_head, gate_act;       // gate_act 0 none, 1 sigmoid, 2 silu
+    float eps, mult;
+};
+
+__global__ void __launch_bounds__(256) linear_finish_kernel(LinFinishArgs a) {
+    __shared__ float red[8];
+    __shared__ float inv_s[256];
+    const int t = blockIdx.x, n = a.H * a.Dv, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* o = a.o + (size_t)t * a.ldo;
+    const float* g = a.gate ? a.gate + (size_t)t * a.ldg + a.g_off : nullptr;
+    if (a.per_head) {
+        for (int h0 = 0; h0 < a.H; h0 += 256) {
+            __syncthreads();
+            for (int h = h0 + warp; h < min(a.H, h0 + 256); h += 8) {
+                float ss = 0.f;
+                for (int d = lane; d < a.Dv; d += 32) { const float v = o[(size_t)h * a.Dv + d]; ss = fmaf(v, v, ss); }
+                ss = warp_sum(ss);
+                if (lane == 0) inv_s[h - h0] = 1.f / sqrtf(ss / (float)a.Dv + a.eps);
+            }
+            __syncthreads();
+            const int lim = min(a.H, h0 + 256) * a.Dv;
+            for (int i = h0 * a.Dv + threadIdx.x; i < lim; i += 256) {
+                float v = o[i] * inv_s[i / a.Dv - h0];
+                if (a.w) v *= a.w[i];
+                if (a.gate_act == 1) v *= sigmoid_f(g[i]); else if (a.gate_act == 2) v *= silu_f(g[i]);
+                o[i] = v * a.mult;
+            }
+        }
+        return;
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) { const float v = o[i]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.f / sqrtf(tot / (float)n + a.eps);
+    for (int i = threadIdx.x; i < n; i += 256) {
+        float v = o[i] * inv;
+        if (a.w) v *= a.w[i];
+        if (a.gate_act == 1) v *= sigmoid_f(g[i]); else if (a.gate_act == 2) v *= silu_f(g[i]);
+        o[i] = v * a.mult;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int pgk_causal_conv_rows_f32(const float* h, float* u, const float* weight, float* state, const int32_t* slot,
+                             const int32_t* pos, int rows, int width, int taps, void* stream) {
+    PGK_REQUIRE(taps >= 1 && width > 0 && (taps == 1 || state), "causal_conv_rows failed: taps %d, width %d", taps, width);
+    PGK_REQUIRE(h != u, "causal_conv_rows failed: the output rows must not be the input rows");
+    if (rows <= 0) return 0;
+    ConvArgs a{h, u, weight, state, slot, pos, width, taps};
+    PGK_CUDA(launch(causal_conv_rows_kernel, dim3(rows, (width + 255) / 256), dim3(256), 0, (cudaStream_t)stream, a));
+    return 0;
+}
+
+int pgk_causal_conv_state_f32(const float* h, float* state, const int32_t* seqs, int n_seqs, int width, int taps, void* stream) {
+    PGK_REQUIRE(taps >= 1 && width > 0, "causal_conv_state failed: taps %d, width %d", taps, width);
+    if (n_seqs <= 0 || taps == 1) return 0;
+    PGK_CUDA(launch(causal_conv_state_kernel, dim3(n_seqs * (taps - 1), (width + 255) / 256), dim3(256), 0, (cudaStream_t)stream,
+                    h, state, (const int4*)seqs, width, taps - 1));
+    return 0;
+}
+
+int pgk_seq_linear_prep(float* proj, int ld, int tokens, int heads, int dim, int vdim, int q_off, int k_off, int v_off,
+                        int activation, int rot_dims, const double* inv_freq, float k_scale, const int32_t* pos, void* stream) {
+    PGK_REQUIRE(heads > 0 && dim > 0 && vdim > 0, "seq_linear_prep failed: invalid head layout");
+    PGK_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || inv_freq),
+                "seq_linear_prep failed: %d rotated dimensions in heads of %d", rot_dims, dim);
+    if (tokens <= 0 || (!activation && rot_dims == 0 && k_scale == 1.f)) return 0;
+    LinPrepArgs a{proj, ld, heads, dim, vdim, q_off, k_off, v_off, activation ? 1 : 0, rot_dims, inv_freq, k_scale, pos};
+    PGK_CUDA(launch(linear_prep_kernel, dim3(tokens, (3 * heads + 3) / 4), dim3(128), 0, (cudaStream_t)stream, a));
+    return 0;
+}
+
+int pgk_seq_linear_value_slice(int heads, int dim, int vdim, int n_seqs) {
+    // value columns per block: as narrow as fills the GPU, never below 8, and S [dim][slice] + the chunk within shared memory
+    int ds = vdim;
+    while (ds > 8 && (long long)n_seqs * heads * ((vdim + ds - 1) / ds) < 2 * 148) ds = (ds + 1) / 2;
+    while (ds > 1 && sizeof(float) * ((size_t)dim * ds + 2 * LC * (dim + 1) + LC * ds + LC * (LC + 1) + LC + 1) > 160 * 1024) ds = (ds + 1) / 2;
+    return ds;
+}
+
+int pgk_seq_linear_attention(const float* proj, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
+                             const float* decay, const int32_t* seqs, int n_seqs, int heads, int dim, int vdim, int value_slice,
+                             void* stream) {
+    PGK_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && value_slice > 0, "seq_linear_attention failed: invalid head layout");
+    if (n_seqs <= 0) return 0;
+    const int ds = value_slice < vdim ? value_slice : vdim;
+    const size_t smem = sizeof(float) * ((size_t)dim * ds + 2 * LC * (dim + 1) + LC * ds + LC * (LC + 1) + LC + 1);
+    PGK_REQUIRE(smem <= 200 * 1024, "seq_linear_attention failed: heads of %d x %d need %zu bytes of shared memory", dim, ds, smem);
+    static bool configured = false;
+    if (smem > 40 * 1024 && !configured) {
+        PGK_CUDA(cudaFuncSetAttribute(linear_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured = true;
+    }
+    LinArgs a{proj, ld, q_off, k_off, v_off, out, ldo, state, decay, (const int4*)seqs, heads, dim, vdim, ds};
+    PGK_CUDA(launch(linear_attention_kernel, dim3(n_seqs, heads, (vdim + ds - 1) / ds), dim3(256), smem, (cudaStream_t)stream, a));
+    return 0;
+}
+
+int pgk_seq_linear_finish(float* o, int ldo, const float* gate_rows, int ldg, int gate_off, const float* weight, int tokens,
+                          int heads, int vdim, int per_head, int gate_act, float eps, float mult, void* stream) {
+    PGK_REQUIRE(heads > 0 && vdim > 0 && gate_act >= 0 && gate_act <= 2 && (gate_act == 0 || gate_rows),
+                "seq_linear_finish failed: invalid arguments");
+    if (tokens <= 0) return 0;
+    LinFinishArgs a{o, ldo, gate_rows, ldg, gate_off, weight, heads, vdim, per_head ? 1 : 0, gate_act, eps, mult};
+    PGK_CUDA(launch(linear_finish_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, a));
+    return 0;
+}
+
+}  // extern "C"

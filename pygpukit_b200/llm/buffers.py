@@ -100,7 +100,7 @@ class RowBuffers:
                 hout = max(hout, m.heads * m.vdim)
             else:
                 attn = max(attn, m.attn_cols)
-                gv = max(gv, m.kv_heads * m.vdim)
+                gv = max(gv, m.kv_heads * getattr(m, "vdim", 0))
             if L.mlp is not None and L.mlp.kind == "dense":
                 sff = max(sff, L.mlp.ff)
             elif L.mlp is not None:
@@ -109,8 +109,8 @@ class RowBuffers:
         R = self.rows = max(8, int(rows))
         self.x = GPUArray((R, W), float32)
         self.y = GPUArray((R, W), float32)
-        parallel = getattr(config, "block", "post_norm") == "parallel"
-        self.h = GPUArray((R, W), float32) if parallel else None                        # the block's normed rows
+        normed = getattr(config, "block", "post_norm") in ("parallel", "pre_norm")
+        self.h = GPUArray((R, W), float32) if normed else None                          # the block's normed rows
         self.x0 = GPUArray((R, W), float32) if getattr(config, "loop_times", 1) > 1 else None   # embedding output
         self.side = GPUArray((R, max(1, getattr(config, "side_dim", 0))), float32)
         self.proj = GPUArray((R, proj), float32)

@@ -241,7 +241,13 @@ class AttentionMixerSpec:
     normalised head by head with one weight vector of size dim; "all": over the whole projection with weights of the
     projection's size.  `qk_bias`: the q and k projections have biases.  `values` "own": a value projection; "keys": the
     values are the keys as projected, before their norm (no value matrix; vdim == dim).  `gate_per_head`: the output
-    gate is one number per head instead of one per output element."""
+    gate is one number per head instead of one per output element.
+
+    `keep_first` > 0 (with a window): the first positions of a sequence stay visible from every later query.
+    `distance_bias` "slopes": the fixed per-head slopes above (True means the same); "log": r1_h ln(1 + r2_h (i - j)) with two
+    learned numbers per head.  `rot`: rotary positions on q and k (a RotarySpec).  `norm_scope` "head" with
+    `norm_weight` False divides q and k by their root mean square and multiplies by nothing.  `weights` "softmax", or
+    "sigmoid": the weight of a visible key is sigmoid(score + b_h) with a learned number per head, not normalised."""
     heads: int
     kv_heads: int
     dim: int
@@ -259,6 +265,10 @@ class AttentionMixerSpec:
     qk_bias: bool = False
     values: str = "own"
     gate_per_head: bool = False
+    keep_first: int = 0
+    rot: "RotarySpec | None" = None
+    norm_weight: bool = True
+    weights: str = "softmax"
 
     kind = "attention"
 
@@ -282,7 +292,107 @@ class AttentionMixerSpec:
 
     def slopes(self) -> list[float]:
         """slope of head h = 2^(-8 (h + 1) / H)"""
-        return [2.0 ** (-8.0 * (h + 1) / self.heads) for h in range(self.heads)] if self.distance_bias else []
+        return ([2.0 ** (-8.0 * (h + 1) / self.heads) for h in range(self.heads)]
+                if self.distance_bias in (True, "slopes") else [])
+
+    state_shapes = ()                    # no per-sequence state beside the cache pages
+
+
+@dataclass(frozen=True)
+class RotarySpec:
+    """Rotary positions in the half layout: of the first `dims` elements of a head, element i is paired with element
+    i + dims / 2 and the pair turns by position * base^(-2 i / dims) / factor (`factor`: linear position scaling)."""
+    dims: int
+    base: float
+    factor: float = 1.0
+
+    def inv_freq(self) -> list[float]:
+        return [self.base ** (-2.0 * i / self.dims) / self.factor for i in range(self.dims // 2)]
+
+
+@dataclass(frozen=True)
+class LinearMixerSpec:
+    """Linear attention with a fixed decay per head and a float32 state per sequence instead of cache pages:
+    S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; H heads, keys of size `dim`, values of size `vdim`.
+    `activation` "silu" / "none" on q, k and v; `rot`: rotary positions on q and k; `k_scale` multiplies k after the
+    rotation; `out_norm` "all": the heads' outputs are divided by their common root mean square and multiplied by a weight
+    vector, "head": every head by its own, no weight; `gate` "sigmoid" / "silu" of a gate projection multiplies the result."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: tuple
+    activation: str = "none"
+    rot: "RotarySpec | None" = None
+    k_scale: float = 1.0
+    out_norm: str = "head"
+    gate: str = "sigmoid"
+
+    kind = "linear_attention"
+    kv_heads = 0
+    chunk = 0
+    window = 0
+    keep_first = 0
+
+    @property
+    def proj_cols(self) -> int:
+        """columns of the fused projection [q | k | v | gate]"""
+        return 2 * self.heads * self.dim + 2 * self.heads * self.vdim
+
+    @property
+    def attn_cols(self) -> int:
+        return self.heads * self.vdim
+
+    def cache_shape(self) -> tuple[int, int, int]:
+        return (0, 0, 0)                 # no cache pages
+
+    @property
+    def state_shapes(self) -> tuple:
+        """float32 elements per sequence slot of every state array"""
+        return (self.heads * self.dim * self.vdim,)
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side on the same input: left_scale * left + right_scale * right (an attention mixer with cache
+    pages and a linear-attention mixer with a state)."""
+    left: AttentionMixerSpec
+    right: LinearMixerSpec
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+
+    kind = "parallel"
+    chunk = 0
+
+    @property
+    def heads(self) -> int:
+        return self.left.heads
+
+    @property
+    def kv_heads(self) -> int:
+        return self.left.kv_heads
+
+    @property
+    def window(self) -> int:
+        return self.left.window
+
+    @property
+    def keep_first(self) -> int:
+        return self.left.keep_first
+
+    @property
+    def proj_cols(self) -> int:
+        return self.left.proj_cols + self.right.proj_cols
+
+    @property
+    def attn_cols(self) -> int:
+        return self.left.attn_cols + self.right.attn_cols
+
+    def cache_shape(self) -> tuple[int, int, int]:
+        return self.left.cache_shape()
+
+    @property
+    def state_shapes(self) -> tuple:
+        return self.right.state_shapes
 
 
 @dataclass(frozen=True)
@@ -309,6 +419,8 @@ class LatentMixerSpec:
     kv_heads = 1
     chunk = 0
     window = 0
+    keep_first = 0
+    state_shapes = ()
 
     @property
     def gate_cols(self) -> int:
@@ -335,7 +447,8 @@ class LatentMixerSpec:
 @dataclass(frozen=True)
 class DenseSpec:
     """Gated dense feed-forward: g = W_gate h, u = W_up h, output W_down act(g, u).  activation "silu": silu(g) u;
-    "clamped_swish": g <- min(g, limit), u <- clamp(u, -limit, limit), g sigmoid(alpha g) (u + 1)."""
+    "clamped_swish": g <- min(g, limit), u <- clamp(u, -limit, limit), g sigmoid(alpha g) (u + 1).  "relu2" has no gate:
+    W_down max(W_up h, 0)^2."""
     ff: int
     activation: str = "silu"
     limit: float = 0.0
@@ -363,7 +476,7 @@ class MoESpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    mixer: "AttentionMixerSpec | LatentMixerSpec"
+    mixer: "AttentionMixerSpec | LatentMixerSpec | LinearMixerSpec | ParallelMixerSpec"
     mlp: "MoESpec | DenseSpec | None"
 
 
@@ -378,9 +491,12 @@ class LayeredConfig:
     norm_eps: float = 1e-5
     logit_scale: float = 1.0
     logit_softcap: float = 0.0
-    # block form: "post_norm" x += LN(sublayer(x)) twice; "parallel" h = norm(x), x += s1 mixer(h) + s2 ff(h)
+    # block form: "post_norm" x += LN(sublayer(x)) twice; "parallel" h = norm(x), x += s1 mixer(h) + s2 ff(h);
+    # "pre_norm" x += m mixer(c1(norm1(x))), x += m ff(c2(norm2(x))) with m = residual_mult and c the input convolution
     block: str = "post_norm"
-    norm: str = "layernorm"            # "layernorm" (weight + bias) or "rmsnorm_1p" (x / rms * (1 + w))
+    norm: str = "layernorm"            # "layernorm" (weight + bias), "layernorm_nobias" or "rmsnorm_1p" (x / rms * (1 + w))
+    residual_mult: float = 1.0         # pre_norm blocks: factor on every sublayer's result before it joins the residual
+    conv_taps: int = 0                 # > 0: h <- h + causal convolution over `conv_taps` positions in front of every sublayer
     embed_norm: bool = False           # the model's norm on the embedding output
     layer_scale: bool = False          # per-channel factors on the mixer's and the feed-forward's result
     side_dim: int = 0                  # > 0: a per-layer token input of this size after every layer
@@ -487,8 +603,80 @@ def _turutar_config(d: dict) -> LayeredConfig:
                          loop_start=start, loop_stop=stop, loop_times=times)
 
 
+def _rotary(rot: dict | None, dim: int, where: str) -> RotarySpec | None:
+    if not rot:
+        return None
+    dims = int(rot.get("dims", dim))
+    if dims % 2 or not 0 < dims <= dim:
+        raise ValueError(f"{where}: {dims} rotated dimensions in heads of {dim}")
+    return RotarySpec(dims=dims, base=float(rot.get("base", 10000.0)), factor=float((rot.get("scaling") or {}).get("factor", 1.0)))
+
+
+def _rezulorn_config(d: dict) -> LayeredConfig:
+    """Rezulorn: pre-norm blocks (LayerNorm without bias, a short causal convolution in front of every sublayer, one factor
+    on every sublayer's result) of three mixers -- "lightning" (decayed linear attention on SiLU features, common output
+    norm, sigmoid gate), "attention" (sliding window with kept first positions, logarithmic distance term, softmax) and
+    "parallel" (sigmoid-weighted rotary attention with unit-norm q / k beside rotary retention with per-head output norm
+    and SiLU gate) -- and a squared-ReLU feed-forward.  What the design fixes is set here; sizes and constants come from
+    the file."""
+
+    def heads_of(m, where):
+        heads, dim = int(m["heads"]), int(m["dim"])
+        kv = int(m.get("kv_heads") or heads)
+        if heads < 1 or dim < 1 or heads % kv:
+            raise ValueError(f"{where}: {heads} heads over {kv} key/value heads")
+        return heads, kv, dim, int(m.get("vdim") or dim)
+
+    def decays(m, heads, where):
+        dec = tuple(float(v) for v in m["decay"])
+        if len(dec) != heads:
+            raise ValueError(f"{where}: {len(dec)} decays for {heads} heads")
+        return dec
+
+    layers = []
+    for i, L in enumerate(d["layers"]):
+        m, kind, where = L["mixer"], L.get("type"), f"Rezulorn: layer {i}"
+        if kind == "lightning":
+            heads, _, dim, vdim = heads_of(m, where)
+            mixer = LinearMixerSpec(heads=heads, dim=dim, vdim=vdim, decay=decays(m, heads, where), activation="silu",
+                                    out_norm="all", gate="sigmoid")
+        elif kind == "attention":
+            heads, kv, dim, vdim = heads_of(m, where)
+            mask = m.get("mask") or {}
+            mixer = AttentionMixerSpec(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=float(m["scale"]),
+                                       window=int(mask.get("size") or 0), keep_first=int(mask.get("keep_first") or 0),
+                                       qk_norm=False, out_gate=False, distance_bias="log")
+        elif kind == "parallel":
+            lm, rm = m["left"], m["right"]
+            heads, kv, dim, vdim = heads_of(lm, where + " (left)")
+            left = AttentionMixerSpec(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=float(lm["scale"]), qk_norm=True,
+                                      norm_weight=False, out_gate=False, distance_bias=False,
+                                      rot=_rotary(lm.get("rot"), dim, where + " (left)"), weights="sigmoid")
+            heads, _, dim, vdim = heads_of(rm, where + " (right)")
+            right = LinearMixerSpec(heads=heads, dim=dim, vdim=vdim, decay=decays(rm, heads, where + " (right)"),
+                                    rot=_rotary(rm.get("rot"), dim, where + " (right)"), k_scale=dim ** -0.5, out_norm="head",
+                                    gate="silu")
+            mixer = ParallelMixerSpec(left, right, float(m.get("left_scale", 1.0)), float(m.get("right_scale", 1.0)))
+        else:
+            raise ValueError(f"{where} has unknown type {kind!r}")
+        mlp = None
+        f = L.get("mlp")
+        if f:
+            if f.get("kind") != "dense":
+                raise ValueError(f"{where} has unknown feed-forward kind {f.get('kind')!r}")
+            mlp = DenseSpec(ff=int(f["ff"]), activation="relu2")
+        layers.append(LayerSpec(mixer, mlp))
+    taps = int((d.get("canon") or {}).get("taps") or 0)
+    if taps < 0:
+        raise ValueError(f"Rezulorn: {taps} convolution taps")
+    return LayeredConfig(architecture="Rezulorn", vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), layers=layers,
+                         norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)), logit_scale=float(d.get("logit_scale") or 1.0),
+                         block="pre_norm", norm="layernorm_nobias", residual_mult=float(d.get("residual_mult", 1.0)),
+                         conv_taps=taps)
+
+
 # config.json "architecture" -> parser (the model registry of the layered families)
-LAYERED_ARCHITECTURES = {"dolurax": _dolurax_config, "turutar": _turutar_config}
+LAYERED_ARCHITECTURES = {"dolurax": _dolurax_config, "turutar": _turutar_config, "rezulorn": _rezulorn_config}
 
 
 def layered_config_from_json(d: dict) -> LayeredConfig | None:
@@ -499,5 +687,5 @@ def layered_config_from_json(d: dict) -> LayeredConfig | None:
 
 __all__ = ["ModelSpec", "TransformerConfig", "GPT2Config", "LlamaConfig", "Qwen3Config", "GPT2_SPEC", "LLAMA_SPEC",
            "QWEN2_SPEC", "QWEN3_SPEC", "QWEN3_MOE_SPEC", "MIXTRAL_SPEC", "MODEL_SPECS", "detect_model_spec",
-           "named_config", "AttentionMixerSpec", "LatentMixerSpec", "DenseSpec", "MoESpec", "LayerSpec", "LayeredConfig",
+           "named_config", "AttentionMixerSpec", "LatentMixerSpec", "RotarySpec", "LinearMixerSpec", "ParallelMixerSpec", "DenseSpec", "MoESpec", "LayerSpec", "LayeredConfig",
            "LAYERED_ARCHITECTURES", "layered_config_from_json"]

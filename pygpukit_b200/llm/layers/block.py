@@ -155,4 +155,55 @@ class ParallelBlock:
         return n
 
 
-__all__ = ["TransformerBlock", "PostNormBlock", "ParallelBlock"]
+class PreNormBlock:
+    """Block of the token-major models with a norm in front of EACH sublayer: x += m * mixer(c1(norm1(x))), then
+    x += m * ff(c2(norm2(x))); c1 / c2 are optional short causal convolutions over time on the normed rows
+    (`CausalConvRows`), m one factor for both sublayers.  The two scaled adds ride in the epilogues of the output projection
+    and of the down projection (C += m * product).  Per-sequence state of the block, in this order in the cache manager:
+    the rings of c1 and c2, then whatever the mixer keeps."""
+
+    def __init__(self, norm1, conv1, mixer, norm2, conv2, mlp, mult: GPUArray):
+        """mult: [width] floats, every element the residual factor m (the epilogue takes a factor per column)."""
+        self.norm1, self.conv1, self.mixer, self.norm2, self.conv2, self.mlp, self.mult = norm1, conv1, mixer, norm2, conv2, mlp, mult
+        if mlp is None and (norm2 is not None or conv2 is not None):
+            raise ValueError("PreNormBlock: a second norm or convolution without a feed-forward")
+        self._convs = [c for c in (conv1, conv2) if c is not None and c.taps > 1]
+
+    norm = None                          # the block's norms are not fused with the block before
+
+    @property
+    def state_shapes(self) -> tuple:
+        return tuple(c.state_size for c in self._convs) + tuple(self.mixer.spec.state_shapes)
+
+    def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None, normed: bool = False,
+                next_norm=None, next_add_ptr: int | None = None) -> bool:
+        if add_ptr is not None:
+            raise ValueError("PreNormBlock: no loop passes in this block form")
+        T, W = ctx.T, x.shape[1]
+        h, u = ctx.buf.h, ctx.buf.y
+        state = list(ctx.cache.state[cache_index]) if cache_index is not None else []
+        rings = {id(c): state.pop(0) for c in self._convs}
+        src = h
+        self.norm1.forward(x.device_ptr, h.device_ptr, T, W)
+        if self.conv1 is not None:
+            self.conv1.forward(ctx, h.device_ptr, u.device_ptr, rings.get(id(self.conv1)))
+            src = u
+        self.mixer.forward(ctx, src, x, cache_index, out_scale=self.mult.device_ptr, state=state)
+        if self.mlp is not None:
+            src = h
+            self.norm2.forward(x.device_ptr, h.device_ptr, T, W)
+            if self.conv2 is not None:
+                self.conv2.forward(ctx, h.device_ptr, u.device_ptr, rings.get(id(self.conv2)))
+                src = u
+            self.mlp.forward(ctx, src.device_ptr, x.device_ptr, out_scale=self.mult.device_ptr)
+        return False
+
+    @property
+    def weight_bytes(self) -> int:
+        n = self.mixer.weight_bytes + self.norm1.nbytes + (self.conv1.nbytes if self.conv1 is not None else 0)
+        if self.mlp is not None:
+            n += self.mlp.weight_bytes + self.norm2.nbytes + (self.conv2.nbytes if self.conv2 is not None else 0)
+        return n
+
+
+__all__ = ["TransformerBlock", "PostNormBlock", "ParallelBlock", "PreNormBlock"]

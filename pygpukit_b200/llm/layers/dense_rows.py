@@ -5,6 +5,9 @@ interleaved (gate_j, up_j) pairs, and the down projection.
   activation "silu":           silu(g) * u
   activation "clamped_swish":  g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1)
 
+`SquaredReluRows` is the feed-forward without a gate, W_down max(W_up h, 0)^2, the activation again in the first product's
+epilogue.
+
 `forward(..., out_scale=ptr)` adds `out_scale * result` to `out` in the down projection's epilogue (layer scale and
 residual add of a parallel block); without it the result is stored.
 """
@@ -39,4 +42,26 @@ class GatedDenseRows:
             self.down.forward_seq(act.device_ptr, sp.ff, T, out_ptr, self.down.out_features, epilogue=4, col_scale=out_scale)
 
 
-__all__ = ["GatedDenseRows"]
+class SquaredReluRows:
+    def __init__(self, spec: DenseSpec, up: LinearRows, down: LinearRows):
+        if spec.activation != "relu2":
+            raise ValueError(f"SquaredReluRows: activation {spec.activation!r}")
+        if up.out_features != spec.ff or down.in_features != spec.ff:
+            raise ValueError("SquaredReluRows: matrices do not match the feed-forward size")
+        self.spec, self.up, self.down = spec, up, down
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.up.nbytes + self.down.nbytes
+
+    def forward(self, ctx, h_ptr: int, out_ptr: int, out_scale: int | None = None) -> None:
+        sp, T = self.spec, ctx.T
+        W, act = self.up.in_features, ctx.buf.shared_act
+        self.up.forward_seq(h_ptr, W, T, act.device_ptr, sp.ff, epilogue=6)
+        if out_scale is None:
+            self.down.forward_seq(act.device_ptr, sp.ff, T, out_ptr, self.down.out_features, epilogue=0)
+        else:
+            self.down.forward_seq(act.device_ptr, sp.ff, T, out_ptr, self.down.out_features, epilogue=4, col_scale=out_scale)
+
+
+__all__ = ["GatedDenseRows", "SquaredReluRows"]

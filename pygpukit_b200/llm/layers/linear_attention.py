@@ -1,0 +1,130 @@
+"""Mixers with a recurrent state per sequence in the token-major models (net-new; beside `PagedAttentionMixer` and
+`LatentAttentionMixer`, which keep cache pages).
+
+`LinearAttentionMixer`: linear attention with a fixed decay per head, S_t = a_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, the
+state S [heads, dim, vdim] in float32 in a per-slot array of the cache manager (`PagedKVCache.state`).  One fused projection
+[q | k | v | gate], then three launches
+
+  pgk_seq_linear_prep        activation of q / k / v, rotary positions on q and k, the key scale
+  pgk_seq_linear_attention   the recurrence over the step's tokens, chunk by chunk, state read and written once
+  pgk_seq_linear_finish      output norm (all heads together with a weight, or head by head without), gate, constant factor
+
+and the output projection.  Every constant comes from the `LinearMixerSpec`.  `attend` is the mixer without its two matrix
+products, on a block of columns of a wider projection.
+
+`ParallelMixer`: an attention mixer and a linear-attention mixer side by side on the same input,
+left_scale * left + right_scale * right.  Both sides' projections are ONE product, both sides' output projections are ONE
+product over the concatenated head outputs (the two factors ride on the head outputs, where the kernels multiply anyway).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from ..._lib import api
+from ...core.array import GPUArray
+from ...core.factory import from_numpy
+from ...core.stream import current_stream_handle as _st
+from ..config import LinearMixerSpec, ParallelMixerSpec
+from .linear import LinearRows
+from .paged_attention import PagedAttentionMixer
+
+
+class LinearAttentionMixer:
+    queries_per_tile = None              # no attention tiles
+
+    def __init__(self, spec: LinearMixerSpec, layer: int, qkvg: "LinearRows | None", o_proj: "LinearRows | None",
+                 norm_weight: "GPUArray | None", eps: float, out_mult: float = 1.0):
+        s = spec
+        if s.activation not in ("none", "silu") or s.out_norm not in ("all", "head") or s.gate not in ("none", "sigmoid", "silu"):
+            raise ValueError(f"layer {layer}: unknown activation / output norm / gate in {s}")
+        if len(s.decay) != s.heads:
+            raise ValueError(f"layer {layer}: {len(s.decay)} decays for {s.heads} heads")
+        self.spec, self.layer, self.qkvg, self.o_proj = spec, layer, qkvg, o_proj
+        self.norm_weight, self.eps, self.out_mult = norm_weight, float(eps), float(out_mult)
+        self.q_cols = self.k_cols = s.heads * s.dim
+        self.v_cols = s.heads * s.vdim
+        self.proj_cols = s.proj_cols if s.gate != "none" else self.q_cols + self.k_cols + self.v_cols
+        if qkvg is not None and qkvg.out_features != self.proj_cols:
+            raise ValueError(f"layer {layer}: fused projection has {qkvg.out_features} rows, the mixer needs {self.proj_cols}")
+        if norm_weight is not None and norm_weight.size != self.v_cols:
+            raise ValueError(f"layer {layer}: the output norm's weight has {norm_weight.size} elements, not {self.v_cols}")
+        self.decay = from_numpy(np.asarray(s.decay, np.float32))
+        self.inv_freq = from_numpy(np.asarray(s.rot.inv_freq(), np.float64)) if s.rot is not None else None
+
+    @property
+    def weight_bytes(self) -> int:
+        return (self.qkvg.nbytes if self.qkvg is not None else 0) + (self.o_proj.nbytes if self.o_proj is not None else 0)
+
+    def key_slices(self, ctx) -> int:
+        return 1
+
+    def forward(self, ctx, x: GPUArray, out: GPUArray, cache_index: int | None = None, out_scale: int | None = None,
+                state=None) -> None:
+        """x [T, W] -> out; with out_scale (device pointer of [W] floats) out += out_scale * result.  state: this mixer's
+        per-slot arrays in the cache manager ([S])."""
+        s, T = self.spec, ctx.T
+        W = self.qkvg.in_features
+        proj, attn = ctx.buf.proj, ctx.buf.attn
+        ld, ldo = self.proj_cols, self.v_cols
+        self.qkvg.forward(x.device_ptr, W, T, proj.device_ptr, ld)
+        self.attend(ctx, proj.device_ptr, ld, attn.device_ptr, ldo, state)
+        if out_scale is None:
+            self.o_proj.forward(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features)
+        else:
+            self.o_proj.forward_seq(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features, epilogue=4,
+                                    col_scale=out_scale)
+
+    def attend(self, ctx, proj_ptr: int, ld: int, attn_ptr: int, ldo: int, state) -> None:
+        s, T = self.spec, ctx.T
+        if not state:
+            raise ValueError(f"layer {self.layer}: the linear-attention mixer needs its state array")
+        k_off, v_off = self.q_cols, self.q_cols + self.k_cols
+        api.seq_linear_prep(proj_ptr, ld, T, s.heads, s.dim, s.vdim, 0, k_off, v_off, 1 if s.activation == "silu" else 0,
+                            s.rot.dims if s.rot is not None else 0,
+                            self.inv_freq.device_ptr if self.inv_freq is not None else None, float(s.k_scale), ctx.pos_ptr, _st())
+        seqs_ptr, n_seqs = ctx.seqs()
+        ds = int(api.seq_linear_value_slice(s.heads, s.dim, s.vdim, n_seqs))
+        api.seq_linear_attention(proj_ptr, ld, 0, k_off, v_off, attn_ptr, ldo, state[0].device_ptr, self.decay.device_ptr,
+                                 seqs_ptr, n_seqs, s.heads, s.dim, s.vdim, ds, _st())
+        gate_act = {"none": 0, "sigmoid": 1, "silu": 2}[s.gate]
+        api.seq_linear_finish(attn_ptr, ldo, proj_ptr if gate_act else None, ld, v_off + self.v_cols,
+                              self.norm_weight.device_ptr if self.norm_weight is not None else None, T, s.heads, s.vdim,
+                              1 if s.out_norm == "head" else 0, gate_act, self.eps, self.out_mult, _st())
+
+
+class ParallelMixer:
+    def __init__(self, spec: ParallelMixerSpec, layer: int, proj: LinearRows, o_proj: LinearRows, left: PagedAttentionMixer,
+                 right: LinearAttentionMixer):
+        """proj: rows [left q | k | v | right q | k | v | gate]; o_proj: columns [left heads | right heads]; left / right
+        carry the two factors as their `out_mult`."""
+        self.spec, self.layer, self.proj, self.o_proj, self.left, self.right = spec, layer, proj, o_proj, left, right
+        self.proj_cols = left.proj_cols + right.proj_cols
+        self.attn_cols = spec.attn_cols
+        if proj.out_features != self.proj_cols or o_proj.in_features != self.attn_cols:
+            raise ValueError(f"layer {layer}: the fused products do not match the two mixers")
+        self.queries_per_tile = left.queries_per_tile
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.proj.nbytes + self.o_proj.nbytes
+
+    def key_slices(self, ctx) -> int:
+        return self.left.key_slices(ctx)
+
+    def forward(self, ctx, x: GPUArray, out: GPUArray, cache_index: int | None = None, out_scale: int | None = None,
+                state=None) -> None:
+        T, W = ctx.T, self.proj.in_features
+        proj, attn = ctx.buf.proj, ctx.buf.attn
+        ld, ldo = self.proj_cols, self.attn_cols
+        self.proj.forward(x.device_ptr, W, T, proj.device_ptr, ld)
+        self.left.attend(ctx, proj.device_ptr, ld, attn.device_ptr, ldo, cache_index)
+        self.right.attend(ctx, proj.device_ptr + 4 * self.left.proj_cols, ld, attn.device_ptr + 4 * self.spec.left.attn_cols,
+                          ldo, state)
+        if out_scale is None:
+            self.o_proj.forward(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features)
+        else:
+            self.o_proj.forward_seq(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features, epilogue=4,
+                                    col_scale=out_scale)
+
+
+__all__ = ["LinearAttentionMixer", "ParallelMixer"]

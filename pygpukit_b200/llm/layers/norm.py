@@ -26,16 +26,18 @@ class Norm:
 
 
 class RowNorm:
-    """Norm of float32 rows in the token-major models: "layernorm" (weight, bias) or an RMS norm whose weight enters as
+    """Norm of float32 rows in the token-major models: "layernorm" (weight, bias; "layernorm_nobias": weight alone) or an RMS norm whose weight enters as
     (offset + weight) -- offset 1 for weights stored around zero, 0 for plain ones.  `forward` can gather its rows
     (final norm of the wanted rows), add a second summand first and write the sum back (the start of a loop pass), or
     accumulate into the output (a normalised branch added to the residual stream)."""
 
     def __init__(self, kind: str, weight: GPUArray, bias: GPUArray | None = None, eps: float = 1e-5, offset: float = 0.0):
-        if kind not in ("layernorm", "rmsnorm"):
+        if kind not in ("layernorm", "layernorm_nobias", "rmsnorm"):
             raise ValueError(f"RowNorm: unknown kind {kind!r}")
         if kind == "layernorm" and bias is None:
             raise ValueError("RowNorm: LayerNorm requires a bias")
+        if kind == "layernorm_nobias":
+            kind, bias = "layernorm", None
         self.kind, self.weight, self.bias, self.eps, self.offset = kind, weight, bias, float(eps), float(offset)
 
     @property
@@ -52,8 +54,9 @@ class RowNorm:
             return
         if add_ptr is not None or sum_out_ptr is not None:
             raise ValueError("RowNorm: a LayerNorm row takes no second summand")
-        api.combine_layernorm_f32(x_ptr, src_rows, None, None, None, 0, self.weight.device_ptr, self.bias.device_ptr,
-                                  self.eps, out_ptr, rows, width, 1 if accumulate else 0, _st())
+        api.combine_layernorm_f32(x_ptr, src_rows, None, None, None, 0, self.weight.device_ptr,
+                                  self.bias.device_ptr if self.bias is not None else None, self.eps, out_ptr, rows, width,
+                                  1 if accumulate else 0, _st())
 
 
     def forward_seam(self, y_ptr: int, x_ptr: int, nxt: "RowNorm", h_ptr: int, rows: int, width: int,
@@ -69,4 +72,33 @@ class RowNorm:
         return nxt is not None and self.kind == "rmsnorm" and nxt.kind == "rmsnorm" and self.eps == nxt.eps
 
 
-__all__ = ["Norm", "RowNorm"]
+class CausalConvRows:
+    """Short causal convolution over time in front of a sublayer of the token-major models: u_t = h_t + sum_j w[:, j]
+    h_(t - taps + 1 + j), channel by channel, zeros before the sequence's start.  The last taps - 1 inputs of every sequence
+    are state: a ring of taps - 1 rows per slot in the cache manager (`state_size` float32 elements per slot).  Two launches:
+    the rows, then the ring update (rows of the same launch still read the old ring)."""
+
+    def __init__(self, weight: GPUArray):
+        self.weight = weight                                  # [width, taps] float32
+        self.width, self.taps = weight.shape
+
+    @property
+    def state_size(self) -> int:
+        return max(0, self.taps - 1) * self.width
+
+    @property
+    def nbytes(self) -> int:
+        return self.weight.nbytes
+
+    def forward(self, ctx, h_ptr: int, u_ptr: int, state: "GPUArray | None") -> None:
+        from ..._lib import api
+        from ...core.stream import current_stream_handle as _st
+        sp = state.device_ptr if state is not None else None
+        api.causal_conv_rows_f32(h_ptr, u_ptr, self.weight.device_ptr, sp, ctx.slot_ptr, ctx.pos_ptr, ctx.T, self.width,
+                                 self.taps, _st())
+        if self.taps > 1:
+            seqs_ptr, n_seqs = ctx.seqs()
+            api.causal_conv_state_f32(h_ptr, sp, seqs_ptr, n_seqs, self.width, self.taps, _st())
+
+
+__all__ = ["Norm", "RowNorm", "CausalConvRows"]

@@ -18,6 +18,11 @@ l<i>.ls1, l<i>.ls2, l<i>.mlp.{gate,up,down}, l<i>.side.{gate,proj,norm}; windowe
 l<i>.mix.{dq,uq,dkv,uk,uv,g,o}, .dq.norm, .dkv.norm, .sink.  The projections that read the block's normed rows are fused
 row-wise ([q | k | g] and [dq | dkv | g]); uk is stored per head transposed ([heads, kv_rank, dim]) so that the query
 absorbs it, uv as the stack [heads, vdim, kv_rank].
+
+Rezulorn tensor names: embed, final.norm, head; per layer l<i>.norm1, l<i>.norm2, l<i>.canon1, l<i>.canon2 [width, taps],
+l<i>.mlp.{up,down}; "lightning" l<i>.mix.{q,k,v,g,o,norm}; "attention" l<i>.mix.{q,k,v,o,r1,r2}; "parallel"
+l<i>.mix.left.{q,k,v,o,pb} and l<i>.mix.right.{q,k,v,g,o}.  The projections of a mixer are fused row-wise ([q | k | v | g],
+both sides of a parallel mixer in one matrix) and the two output projections of a parallel mixer column-wise.
 """
 from __future__ import annotations
 
@@ -30,12 +35,13 @@ from ..core.array import GPUArray
 from ..core.dtypes import bf16_bits_to_f32, f32_to_bf16_bits
 from ..core.factory import from_numpy
 from .config import LayeredConfig, layered_config_from_json
-from .layers.block import ParallelBlock, PostNormBlock
-from .layers.dense_rows import GatedDenseRows
+from .layers.block import ParallelBlock, PostNormBlock, PreNormBlock
+from .layers.dense_rows import GatedDenseRows, SquaredReluRows
+from .layers.linear_attention import LinearAttentionMixer, ParallelMixer
 from .layers.latent_attention import LatentAttentionMixer
 from .layers.linear import LinearRows, interleave_gate_up
 from .layers.moe_rows import GroupedRouterMoE
-from .layers.norm import RowNorm
+from .layers.norm import CausalConvRows, RowNorm
 from .layers.paged_attention import PagedAttentionMixer
 from .layers.token_side import TokenSideInput
 from .models.layered import LayeredCausalModel
@@ -179,8 +185,62 @@ def _build_dolurax(config: LayeredConfig, t: _Tensors, dtype: str) -> LayeredCau
     return LayeredCausalModel(config, _matrix(t.f32("embed", (V, W)), dtype), blocks, final, head, dtype)
 
 
+def _build_rezulorn(config: LayeredConfig, t: _Tensors, dtype: str) -> LayeredCausalModel:
+    W, V, eps, taps = config.hidden_size, config.vocab_size, config.norm_eps, config.conv_taps
+    mult = _vector(np.full((W,), config.residual_mult, np.float32))
+
+    def norm(name):
+        return RowNorm("layernorm_nobias", _vector(t.f32(name, (W,))), None, eps)
+
+    def conv(name):
+        return CausalConvRows(_vector(t.f32(name, (W, taps)))) if taps > 0 else None
+
+    def attention(m, mp, layer, fused: bool, out_mult: float = 1.0):
+        parts = [t.f32(mp + "q", (m.heads * m.dim, W)), t.f32(mp + "k", (m.kv_heads * m.dim, W)),
+                 t.f32(mp + "v", (m.kv_heads * m.vdim, W))]
+        o = t.f32(mp + "o", (W, m.heads * m.vdim))
+        dist = (_vector(t.f32(mp + "r1", (m.heads,))), _vector(t.f32(mp + "r2", (m.heads,)))) if m.distance_bias == "log" else None
+        pb = _vector(t.f32(mp + "pb", (m.heads,))) if m.weights == "sigmoid" else None
+        mixer = PagedAttentionMixer(m, layer, None if fused else LinearRows(_matrix(np.concatenate(parts), dtype)),
+                                    None if fused else LinearRows(_matrix(o, dtype)), None, None, eps, distance=dist,
+                                    weight_bias=pb, out_mult=out_mult)
+        return mixer, parts, o
+
+    def linear(m, mp, layer, fused: bool, out_mult: float = 1.0):
+        parts = [t.f32(mp + "q", (m.heads * m.dim, W)), t.f32(mp + "k", (m.heads * m.dim, W)),
+                 t.f32(mp + "v", (m.heads * m.vdim, W)), t.f32(mp + "g", (m.heads * m.vdim, W))]
+        o = t.f32(mp + "o", (W, m.heads * m.vdim))
+        nw = _vector(t.f32(mp + "norm", (m.heads * m.vdim,))) if m.out_norm == "all" else None
+        mixer = LinearAttentionMixer(m, layer, None if fused else LinearRows(_matrix(np.concatenate(parts), dtype)),
+                                     None if fused else LinearRows(_matrix(o, dtype)), nw, eps, out_mult=out_mult)
+        return mixer, parts, o
+
+    blocks = []
+    for i, L in enumerate(config.layers):
+        p, m = f"l{i}.", L.mixer
+        mp = p + "mix."
+        if m.kind == "linear_attention":
+            mixer = linear(m, mp, i, False)[0]
+        elif m.kind == "attention":
+            mixer = attention(m, mp, i, False)[0]
+        else:
+            left, lp, lo = attention(m.left, mp + "left.", i, True, m.left_scale)
+            right, rp, ro = linear(m.right, mp + "right.", i, True, m.right_scale)
+            mixer = ParallelMixer(m, i, LinearRows(_matrix(np.concatenate(lp + rp), dtype)),
+                                  LinearRows(_matrix(np.concatenate([lo, ro], axis=1), dtype)), left, right)
+        mlp = norm2 = conv2 = None
+        if L.mlp is not None:
+            f, q = L.mlp, p + "mlp."
+            mlp = SquaredReluRows(f, LinearRows(_matrix(t.f32(q + "up", (f.ff, W)), dtype)),
+                                  LinearRows(_matrix(t.f32(q + "down", (W, f.ff)), dtype)))
+            norm2, conv2 = norm(p + "norm2"), conv(p + "canon2")
+        blocks.append(PreNormBlock(norm(p + "norm1"), conv(p + "canon1"), mixer, norm2, conv2, mlp, mult))
+    head = LinearRows(_matrix(t.f32("head", (V, W)), dtype), epilogue=2, scale=config.logit_scale, cap=0.0)
+    return LayeredCausalModel(config, _matrix(t.f32("embed", (V, W)), dtype), blocks, norm("final.norm"), head, dtype)
+
+
 # architecture (lower case) -> builder of its blocks from the checkpoint's tensors
-_BUILDERS = {"dolurax": _build_dolurax, "turutar": _build_turutar}
+_BUILDERS = {"dolurax": _build_dolurax, "turutar": _build_turutar, "rezulorn": _build_rezulorn}
 
 
 def load_layered_model(model_path: str, dtype: str = "bfloat16", config: dict | None = None) -> LayeredCausalModel:

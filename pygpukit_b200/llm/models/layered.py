@@ -75,6 +75,13 @@ class StepContext:
             parts.append(np.asarray(t, np.int32).reshape(-1))
             self._tiles_off[qt] = (cur, len(t))
             cur += 4 * len(t)
+        pad = (-cur) % 4                           # one (first row, rows, slot, first position) per sequence, int4 loads
+        if pad:
+            parts.append(np.zeros(pad, np.int32))
+            cur += pad
+        parts.append(np.asarray(seqs, np.int32).reshape(-1))
+        self._seqs_off = cur
+        cur += 4 * len(seqs)
         meta = np.concatenate(parts)
         self.meta = model._meta_buffer(meta.size)
         api.memcpy_h2d(self.meta.device_ptr, meta.ctypes.data, meta.nbytes, _st())
@@ -86,10 +93,15 @@ class StepContext:
         self.cache = cache
         self.buf = model._buffers(self.T)
 
-    def max_keys(self, chunk: int, window: int = 0) -> int:
-        """The longest key range any tile of the step reads under a chunk size and a window (0: none)."""
+    def max_keys(self, chunk: int, window: int = 0, keep_first: int = 0) -> int:
+        """The longest key range any tile of the step reads under a chunk size and a window (0: none) that keeps the first
+        `keep_first` positions visible."""
         keys = max(p0 + n - ((p0 // chunk) * chunk if chunk > 0 else 0) for _, n, _, p0 in self._seqs)
-        return min(keys, window + 64) if window > 0 else keys
+        return min(keys, window + 64 + keep_first) if window > 0 else keys
+
+    def seqs(self) -> tuple[int, int]:
+        """(device pointer, count) of the step's sequences as (first row, rows, slot, first position)"""
+        return self._base + 4 * self._seqs_off, len(self._seqs)
 
     def workspace(self, n_floats: int) -> GPUArray:
         return self._model._workspace(n_floats)
@@ -128,14 +140,15 @@ class LayeredCausalModel:
         self._graphs: dict = {}
         self._graph_warm: set = set()
         self._gstream: Stream | None = None
-        self._tile_sizes = {b.mixer.queries_per_tile for b in blocks}
+        self._tile_sizes = {b.mixer.queries_per_tile for b in blocks if b.mixer.queries_per_tile}
         self._tops = {b.mlp.spec.top for b in blocks if b.mlp is not None and b.mlp.spec.kind == "moe"}
 
     # ------------------------------------------------------------------ setup
     def init_cache(self, max_tokens: int = 4096, page_size: int = 64, slots: int = 8) -> PagedKVCache:
         """Allocate the paged cache for about `max_tokens` live positions (it grows when more arrive)."""
         shapes = [self.blocks[li].mixer.spec.cache_shape() for li, _ in self.runs]
-        self.cache = PagedKVCache(shapes, self.dtype, page_size, max_tokens, slots)
+        states = [tuple(getattr(self.blocks[li], "state_shapes", ())) for li, _ in self.runs]
+        self.cache = PagedKVCache(shapes, self.dtype, page_size, max_tokens, slots, state_shapes=states)
         self._graphs.clear()
         self._graph_warm.clear()
         return self.cache
@@ -193,7 +206,8 @@ class LayeredCausalModel:
         if not self.use_graphs or ctx.T > LinearRows.FEW or not ctx.decode_only:
             return None
         c = self.cache
-        return (ctx.T, ctx.n_want, c.pool.max_pages, c.table_dev.device_ptr, c.k[0].device_ptr, id(ctx.buf),
+        arrays = tuple(a.device_ptr for a in c.k if a is not None)[:1] + tuple(a.device_ptr for st in c.state for a in st)[:1]
+        return (ctx.T, ctx.n_want, c.pool.max_pages, c.table_dev.device_ptr, arrays, id(ctx.buf),
                 self._meta.device_ptr, self._out.device_ptr, self._ws.device_ptr if self._ws is not None else 0,
                 tuple(blk.mixer.key_slices(ctx) for blk in self.blocks))
 

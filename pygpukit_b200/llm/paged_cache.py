@@ -7,6 +7,11 @@ length.  `PagedKVCache` adds the device side: per layer one K and one V array of
 (bfloat16 or float32) and the int32 page table `[slots, max_pages]` that the kernels read.  Sequences are named by
 any hashable id; `release(id)` gives the slot and the pages back, and both are handed out again (lowest first).
 
+Per-sequence STATE: a layer may keep, beside or instead of pages, float32 arrays with one row per slot (the state of a
+recurrent mixer, the last inputs of a short convolution): `state[i][j]` is `[slots, n]`.  A state row needs no clearing
+when its slot is handed out again -- the kernels that read it take a sequence whose first position is 0 as starting from
+zero -- and cannot be truncated.
+
 Growth: when the free list runs dry the pool doubles (device arrays are reallocated and the old pages copied, page
 numbers stay valid); a page table row grows the same way.  Sizing the pool for the expected number of live tokens up
 front (`tokens_hint`) avoids both.
@@ -126,10 +131,11 @@ class PagePool:
 class PagedKVCache:
     """Device arrays of every layer + the page pool.  `layer_shapes` = [(kv_heads, dim, vdim), ...], one entry per cache
     (a layer that runs several times in a loop has one per run); vdim 0: the layer keeps one array whose rows serve as
-    keys and, by a prefix, as values (latent attention) -- `v[i]` is then None."""
+    keys and, by a prefix, as values (latent attention) -- `v[i]` is then None; kv_heads 0: the layer has no pages at all.
+    `state_shapes` = per cache the float32 elements per slot of each of its state arrays."""
 
     def __init__(self, layer_shapes: list[tuple[int, int, int]], dtype: str = "bfloat16", page_size: int = 64,
-                 tokens_hint: int = 4096, slots: int = 8):
+                 tokens_hint: int = 4096, slots: int = 8, state_shapes: "list[tuple] | None" = None):
         if dtype not in ("bfloat16", "float32"):
             raise ValueError("PagedKVCache: dtype is 'bfloat16' or 'float32'")
         self.dtype = bfloat16 if dtype == "bfloat16" else float32
@@ -137,9 +143,14 @@ class PagedKVCache:
         self.layer_shapes = list(layer_shapes)
         pages = -(-max(1, tokens_hint) // page_size) + slots          # every live sequence may hold one partial page
         self.pool = PagePool(page_size, pages, slots, max(4, -(-max(1, tokens_hint) // page_size) + 1))
-        self.k: list[GPUArray] = []
+        self.k: list[GPUArray | None] = []
         self.v: list[GPUArray | None] = []
         self._alloc(pages, copy_from=None)
+        self.state_shapes = [tuple(int(n) for n in sh) for sh in (state_shapes or [()] * len(self.layer_shapes))]
+        if len(self.state_shapes) != len(self.layer_shapes):
+            raise ValueError("PagedKVCache: one tuple of state sizes per cache")
+        self.state: list[list[GPUArray]] = []
+        self._alloc_state(self.pool.slots, copy_from=None)
         self.table_dev = zeros((self.pool.slots * self.pool.max_pages,), int32)
 
     @property
@@ -150,10 +161,11 @@ class PagedKVCache:
         ps = self.pool.page_size
         k_new, v_new = [], []
         for i, (g, d, dv) in enumerate(self.layer_shapes):
-            k = zeros((pages, g, ps, d), self.dtype)
-            v = zeros((pages, g, ps, dv), self.dtype) if dv > 0 else None
+            k = zeros((pages, g, ps, d), self.dtype) if g > 0 else None
+            v = zeros((pages, g, ps, dv), self.dtype) if dv > 0 and g > 0 else None
             if copy_from is not None:
-                api.memcpy_d2d(k.device_ptr, self.k[i].device_ptr, self.k[i].nbytes, _st())
+                if k is not None:
+                    api.memcpy_d2d(k.device_ptr, self.k[i].device_ptr, self.k[i].nbytes, _st())
                 if v is not None:
                     api.memcpy_d2d(v.device_ptr, self.v[i].device_ptr, self.v[i].nbytes, _st())
             k_new.append(k)
@@ -163,16 +175,39 @@ class PagedKVCache:
         self.k, self.v = k_new, v_new
         self._pages_dev = pages
 
+    def _alloc_state(self, slots: int, copy_from) -> None:
+        new = []
+        for i, sizes in enumerate(self.state_shapes):
+            arrs = []
+            for j, n in enumerate(sizes):
+                a = zeros((slots, n), float32)
+                if copy_from is not None:
+                    api.memcpy_d2d(a.device_ptr, self.state[i][j].device_ptr, self.state[i][j].nbytes, _st())
+                arrs.append(a)
+            new.append(arrs)
+        if copy_from is not None:
+            api.device_sync()
+        self.state = new
+        self._slots_dev = slots
+
+    @property
+    def has_state(self) -> bool:
+        return any(self.state_shapes)
+
     def extend(self, seq_id, n_tokens: int) -> tuple[int, int]:
         out = self.pool.extend(seq_id, n_tokens)
         if self.pool.pages > self._pages_dev:
             self._alloc(self.pool.pages, copy_from=True)
+        if self.pool.slots > self._slots_dev:
+            self._alloc_state(self.pool.slots, copy_from=True)
         return out
 
     def release(self, seq_id) -> None:
         self.pool.release(seq_id)
 
     def truncate(self, seq_id, length: int) -> None:
+        if self.has_state and length != self.pool.length(seq_id):
+            raise ValueError("PagedKVCache: a sequence with recurrent state cannot be cut back")
         self.pool.truncate(seq_id, length)
 
     def sync_table(self) -> None:
@@ -187,7 +222,8 @@ class PagedKVCache:
 
     @property
     def nbytes(self) -> int:
-        return sum(a.nbytes for a in self.k) + sum(a.nbytes for a in self.v if a is not None)
+        return (sum(a.nbytes for a in self.k if a is not None) + sum(a.nbytes for a in self.v if a is not None)
+                + sum(a.nbytes for arrs in self.state for a in arrs))
 
 
 __all__ = ["PagePool", "PagedKVCache"]
