@@ -36,6 +36,9 @@ N > 1 (torchrun): tensor-parallel over N GPUs (strong scaling: the same token st
 An option beside the default workload (whose contract is unchanged): prompt and decode throughput of the layered
 (Dolurax) family at real layer sizes next to Qwen3-MoE at equal sizes, one JSON line (scripts/bench_layered.py).
 
+    python bench.py --rezulorn [--rezulorn-sizes r-2048,r-4096] [--steps K] [--warmup W]
+The same for the Rezulorn design of the layered family beside a dense Dolurax stack at equal sizes.
+
     python bench.py --turutar [--turutar-sizes t-2048,t-4096] [--steps K] [--warmup W]
 The same for the Turutar design (latent + windowed attention, gated dense feed-forward, token side inputs, a looped pair of
 layers) next to a Dolurax stack of equal size, the closest existing model: same family, same cache and kernels.
@@ -90,6 +93,11 @@ def parse_args():
                     help="instead of the default workload: prefill / decode throughput of the Turutar design (latent + windowed "
                          "attention, dense feed-forward, layer loop) beside a Dolurax stack of equal size, one JSON line")
     ap.add_argument("--turutar-sizes", default="t-2048,t-4096")
+    ap.add_argument("--rezulorn", action="store_true",
+                    help="instead of the default workload: prefill / decode throughput of the Rezulorn design (input "
+                         "convolutions, linear attention with per-sequence state, windowed and sigmoid-weighted attention) "
+                         "beside a dense Dolurax stack at equal sizes, one JSON line")
+    ap.add_argument("--rezulorn-sizes", default="r-2048,r-4096")
     return ap.parse_args()
 
 
@@ -615,6 +623,11 @@ def run_ours(args) -> None:
 
 def main():
     args = parse_args()
+    if args.rezulorn:
+        sys.path.insert(0, os.path.join(ROOT, "scripts"))
+        import bench_layered
+        print(json.dumps(bench_layered.main_rezulorn(ROOT, args.rezulorn_sizes.split(","), args.steps, args.warmup)))
+        return
     if args.turutar:
         sys.path.insert(0, os.path.join(ROOT, "scripts"))
         import bench_layered

@@ -575,6 +575,15 @@ int pgk_seq_linear_value_slice(int heads, int dim, int vdim, int n_seqs);
 int pgk_seq_linear_attention(const float* proj, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
                              const float* decay, const int32_t* seqs, int n_seqs, int heads, int dim, int vdim, int value_slice,
                              void* stream);
+/* The same recurrence for long prompts in three launches whose blocks are (chunk of pgk_seq_linear_chunk_tokens tokens,
+ * sequence, head): what every chunk adds to the state, a scan over the chunks per state element, the outputs of every chunk
+ * from the state before it.  One call covers the chunks chunk_begin .. chunk_begin + chunks - 1 of every sequence (sequences
+ * with fewer chunks sit out) and carries the state through the slot's array, so a long prompt can be walked in segments;
+ * workspace: n_seqs x chunks x heads x dim x vdim floats. */
+int pgk_seq_linear_chunk_tokens(void);
+int pgk_seq_linear_attention_chunks(const float* proj, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
+                                    const float* decay, const int32_t* seqs, int n_seqs, int heads, int dim, int vdim,
+                                    int chunk_begin, int chunks, float* workspace, void* stream);
 int pgk_seq_linear_finish(float* o, int ldo, const float* gate_rows, int ldg, int gate_off, const float* weight, int tokens,
                           int heads, int vdim, int per_head, int gate_act, float eps, float mult, void* stream);
 /* mixer_prep for layers whose q / k norm runs over the WHOLE projection: per token, q <- (q + q_bias) / rms(all heads x dim

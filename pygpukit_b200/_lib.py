@@ -131,6 +131,7 @@ _SIGS = {
     "pgk_causal_conv_state_f32": [vp, vp, vp, i32, i32, i32, vp],
     "pgk_seq_linear_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp],
     "pgk_seq_linear_attention": [vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "pgk_seq_linear_attention_chunks": [vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "pgk_seq_linear_finish": [vp, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, f32, f32, vp],
     "pgk_seq_mixer_prep_all": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, f32, f32, vp, vp, i32, vp, i32, i32, vp, vp, vp],
     "pgk_seq_latent_prep": [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, f32, f32, vp, vp, i32, vp, i32, i32, vp, vp, vp],
@@ -147,11 +148,11 @@ _SIGS = {
 _RESTYPE = {"pgk_last_error": C.c_char_p, "pgk_launch_count": i64, "pgk_launch_count_reset": None,
             "pgk_sdpa_workspace_bytes": sz, "pgk_p2p_handle_bytes": sz, "pgk_p2p_ready": i32,
             "pgk_p2p_max_bytes": sz, "pgk_seq_heads_per_block": i32, "pgk_seq_queries_per_tile": i32,
-            "pgk_seq_decode_heads_per_block": i32, "pgk_seq_linear_value_slice": i32}
+            "pgk_seq_decode_heads_per_block": i32, "pgk_seq_linear_value_slice": i32, "pgk_seq_linear_chunk_tokens": i32}
 _EXTRA = {"pgk_last_error": [], "pgk_launch_count": [], "pgk_launch_count_reset": [],
           "pgk_sdpa_workspace_bytes": [i32, i32, i32, i32], "pgk_p2p_handle_bytes": [], "pgk_p2p_ready": [], "pgk_p2p_max_bytes": [],
           "pgk_seq_heads_per_block": [i32, i32], "pgk_seq_queries_per_tile": [i32, i32],
-          "pgk_seq_decode_heads_per_block": [], "pgk_seq_linear_value_slice": [i32, i32, i32, i32]}
+          "pgk_seq_decode_heads_per_block": [], "pgk_seq_linear_value_slice": [i32, i32, i32, i32], "pgk_seq_linear_chunk_tokens": []}
 
 
 def load() -> C.CDLL:

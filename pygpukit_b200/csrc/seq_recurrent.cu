@@ -174,6 +174,179 @@ __global__ void __launch_bounds__(256) linear_attention_kernel(LinArgs a) {
     }
 }
 
+// ---------------------------------------------------------------- linear attention over long prompts: three passes
+// The walk above is sequential over a sequence's chunks.  For prompts the same result comes from three launches whose blocks
+// are (chunk, sequence, head), all chunks at once:
+//   1. chunk_update:  U_c = sum_s a^(n_c - 1 - s) k_s v_s^T, what chunk c adds to the state          -> ws[c]
+//   2. chunk_scan:    per state element, over the chunks in order: ws[c] <- the state BEFORE chunk c, S <- a^(n_c) S + U_c;
+//                     the state after the last chunk goes to the slot's array
+//   3. chunk_output:  o_t = a^(t + 1) S_c^T q_t + sum_{s <= t} (q_t.k_s a^(t - s)) v_s  -- one product of [Q a^(t+1) | A]
+//                     with [S_c ; V], 4 x 4 outputs per thread
+// A launch covers the chunks c_begin .. c_begin + grid.x - 1 of every sequence (the host bounds the workspace by walking
+// long prompts in segments; the scan picks the state up from the slot's array where the segment before left it).
+struct LinChunkArgs {
+    const float* proj; int ld, q_off, k_off, v_off;
+    float* out; int ldo;
+    float* state; const float* decay; const int4* seqs;
+    int H, D, Dv, c_begin;
+    float* ws;                           // [sequences][grid.x chunks][H][D][Dv]
+};
+
+__device__ __forceinline__ int round4(int n) { return (n + 3) & ~3; }
+
+__global__ void __launch_bounds__(256) linear_chunk_update_kernel(LinChunkArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int D = a.D, Dv = a.Dv, D4 = round4(D), V4 = round4(Dv);
+    float* Ks = sm;                      // [LC][D4], rows scaled by a^(nc - 1 - s)
+    float* Vs = Ks + LC * D4;            // [LC][V4]
+    const int4 sq = a.seqs[blockIdx.y];
+    const int c = a.c_begin + blockIdx.x, h = blockIdx.z;
+    if (c * LC >= sq.y) return;
+    const int nc = min(LC, sq.y - c * LC), r0 = sq.x + c * LC, tid = threadIdx.x;
+    const float dec = a.decay[h];
+    for (int i = tid; i < LC * D4; i += 256) {
+        const int s = i / D4, d = i - s * D4;
+        Ks[i] = (s < nc && d < D) ? a.proj[(size_t)(r0 + s) * a.ld + a.k_off + (size_t)h * D + d] * powf(dec, (float)(nc - 1 - s)) : 0.f;
+    }
+    for (int i = tid; i < LC * V4; i += 256) {
+        const int s = i / V4, v = i - s * V4;
+        Vs[i] = (s < nc && v < Dv) ? a.proj[(size_t)(r0 + s) * a.ld + a.v_off + (size_t)h * Dv + v] : 0.f;
+    }
+    __syncthreads();
+    float* U = a.ws + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * a.H + h) * D * Dv;
+    const int nTv = V4 / 4, ntiles = (D4 / 4) * nTv;
+    for (int tile = tid; tile < ntiles; tile += 256) {
+        const int d0 = (tile / nTv) * 4, v0 = (tile % nTv) * 4;
+        float acc[4][4] = {};
+        for (int s2 = 0; s2 < nc; ++s2) {
+            const float4 k4 = *(const float4*)(Ks + s2 * D4 + d0), v4 = *(const float4*)(Vs + s2 * V4 + v0);
+            const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(kk[i], vv[j], acc[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (d0 + i < D && v0 + j < Dv) U[(size_t)(d0 + i) * Dv + v0 + j] = acc[i][j];
+    }
+}
+
+// one thread per (sequence, head, state element)
+__global__ void __launch_bounds__(256) linear_chunk_scan_kernel(LinChunkArgs a, int seg_chunks) {
+    const size_t per = (size_t)a.D * a.Dv, e = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (e >= per) return;
+    const int h = blockIdx.y;
+    const int4 sq = a.seqs[blockIdx.z];
+    const int nchunks = (sq.y + LC - 1) / LC;
+    if (a.c_begin >= nchunks) return;
+    const float dec = a.decay[h], dfull = powf(dec, (float)LC);
+    float* Sg = a.state + ((size_t)sq.z * a.H + h) * per + e;
+    float S = (sq.w > 0 || a.c_begin > 0) ? *Sg : 0.f;
+    const int cend = min(nchunks, a.c_begin + seg_chunks);
+    for (int c = a.c_begin; c < cend; ++c) {
+        float* u = a.ws + (((size_t)blockIdx.z * seg_chunks + (c - a.c_begin)) * a.H + h) * per + e;
+        const int nc = min(LC, sq.y - c * LC);
+        const float add = *u;
+        *u = S;
+        S = fmaf(S, nc == LC ? dfull : powf(dec, (float)nc), add);
+    }
+    *Sg = S;
+}
+
+__global__ void __launch_bounds__(256) linear_chunk_output_kernel(LinChunkArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int D = a.D, Dv = a.Dv, DP = D + 1, V4 = round4(Dv);
+    float* Q = sm;                       // [LC][D + 1]
+    float* K = Q + LC * DP;              // [LC][D + 1]
+    float* Vs = K + LC * DP;             // [LC][V4]
+    float* Ss = Vs + LC * V4;            // [LC][V4]: a slab of state rows
+    float* A = Ss + LC * V4;             // [LC][LC + 1]
+    float* pw = A + LC * (LC + 1);       // [LC + 1]
+    const int4 sq = a.seqs[blockIdx.y];
+    const int c = a.c_begin + blockIdx.x, h = blockIdx.z;
+    if (c * LC >= sq.y) return;
+    const int nc = min(LC, sq.y - c * LC), r0 = sq.x + c * LC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float dec = a.decay[h];
+    if (tid <= LC) pw[tid] = powf(dec, (float)tid);
+    for (int i = tid; i < LC * D; i += 256) {
+        const int r = i / D, d = i - r * D;
+        const float* src = a.proj + (size_t)(r0 + r) * a.ld + (size_t)h * D + d;
+        Q[r * DP + d] = r < nc ? src[a.q_off] : 0.f;
+        K[r * DP + d] = r < nc ? src[a.k_off] : 0.f;
+    }
+    for (int i = tid; i < LC * V4; i += 256) {
+        const int r = i / V4, v = i - r * V4;
+        Vs[i] = (r < nc && v < Dv) ? a.proj[(size_t)(r0 + r) * a.ld + a.v_off + (size_t)h * Dv + v] : 0.f;
+    }
+    __syncthreads();
+    {   // scores: lane = key s, the warp's four rows t = warp + 8 i share every key element
+        float sc[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* k = K + lane * DP;
+        for (int d = 0; d < D; ++d) {
+            const float kv = k[d];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[i] = fmaf(Q[(warp + 8 * i) * DP + d], kv, sc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int t = warp + 8 * i;
+            A[t * (LC + 1) + lane] = lane <= t ? sc[i] * pw[t - lane] : 0.f;
+        }
+    }
+    const float* Sc = a.ws + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * a.H + h) * D * Dv;
+    const int nTv = V4 / 4, ntiles = (LC / 4) * nTv, rounds = (ntiles + 255) / 256;
+    for (int rd = 0; rd < rounds; ++rd) {
+        const int tile = rd * 256 + tid;
+        const bool live = tile < ntiles;
+        const int t0 = live ? (tile / nTv) * 4 : 0, v0 = live ? (tile % nTv) * 4 : 0;
+        float acc[4][4] = {};
+        for (int d0 = 0; d0 < D; d0 += LC) {
+            __syncthreads();
+            for (int i = tid; i < LC * V4; i += 256) {
+                const int r = i / V4, v = i - r * V4;
+                Ss[i] = (d0 + r < D && v < Dv) ? Sc[(size_t)(d0 + r) * Dv + v] : 0.f;
+            }
+            __syncthreads();
+            if (live) {
+                const int nd = min(LC, D - d0);
+                for (int dd = 0; dd < nd; ++dd) {
+                    const float4 s4 = *(const float4*)(Ss + dd * V4 + v0);
+                    const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float q = Q[(t0 + i) * DP + d0 + dd];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(q, ss[j], acc[i][j]);
+                    }
+                }
+            }
+        }
+        if (!live) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] *= pw[t0 + i + 1];
+        for (int s2 = 0; s2 < nc; ++s2) {
+            const float4 v4 = *(const float4*)(Vs + s2 * V4 + v0);
+            const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float w = A[(t0 + i) * (LC + 1) + s2];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(w, vv[j], acc[i][j]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (t0 + i < nc && v0 + j < Dv) a.out[(size_t)(r0 + t0 + i) * a.ldo + (size_t)h * Dv + v0 + j] = acc[i][j];
+    }
+}
+
 // ---------------------------------------------------------------- linear attention: output norm and gate
 struct LinFinishArgs {
     float* o; int ldo; const float* gate; int ldg, g_off;
@@ -281,6 +454,33 @@ int pgk_seq_linear_attention(const float* proj, int ld, int q_off, int k_off, in
     }
     LinArgs a{proj, ld, q_off, k_off, v_off, out, ldo, state, decay, (const int4*)seqs, heads, dim, vdim, ds};
     PGK_CUDA(launch(linear_attention_kernel, dim3(n_seqs, heads, (vdim + ds - 1) / ds), dim3(256), smem, (cudaStream_t)stream, a));
+    return 0;
+}
+
+int pgk_seq_linear_chunk_tokens(void) { return LC; }
+
+int pgk_seq_linear_attention_chunks(const float* proj, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
+                                    const float* decay, const int32_t* seqs, int n_seqs, int heads, int dim, int vdim,
+                                    int chunk_begin, int chunks, float* workspace, void* stream) {
+    PGK_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && chunk_begin >= 0 && workspace, "seq_linear_attention_chunks failed: invalid arguments");
+    if (n_seqs <= 0 || chunks <= 0) return 0;
+    const int D4 = (dim + 3) & ~3, V4 = (vdim + 3) & ~3;
+    const size_t smem1 = sizeof(float) * ((size_t)LC * D4 + (size_t)LC * V4);
+    const size_t smem3 = sizeof(float) * (2 * (size_t)LC * (dim + 1) + 2 * (size_t)LC * V4 + LC * (LC + 1) + LC + 1);
+    PGK_REQUIRE(smem1 <= 200 * 1024 && smem3 <= 200 * 1024, "seq_linear_attention_chunks failed: heads of %d x %d need %zu bytes of shared memory", dim, vdim, smem3);
+    static bool configured = false;
+    if (!configured) {
+        PGK_CUDA(cudaFuncSetAttribute(linear_chunk_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        PGK_CUDA(cudaFuncSetAttribute(linear_chunk_output_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured = true;
+    }
+    LinChunkArgs a{proj, ld, q_off, k_off, v_off, out, ldo, state, decay, (const int4*)seqs, heads, dim, vdim, chunk_begin, workspace};
+    cudaStream_t st = (cudaStream_t)stream;
+    const dim3 grid(chunks, n_seqs, heads);
+    PGK_CUDA(launch(linear_chunk_update_kernel, grid, dim3(256), smem1, st, a));
+    const size_t per = (size_t)dim * vdim;
+    PGK_CUDA(launch(linear_chunk_scan_kernel, dim3((unsigned)((per + 255) / 256), heads, n_seqs), dim3(256), 0, st, a, chunks));
+    PGK_CUDA(launch(linear_chunk_output_kernel, grid, dim3(256), smem3, st, a));
     return 0;
 }
 

@@ -7,6 +7,7 @@ state S [heads, dim, vdim] in float32 in a per-slot array of the cache manager (
 
   pgk_seq_linear_prep        activation of q / k / v, rotary positions on q and k, the key scale
   pgk_seq_linear_attention   the recurrence over the step's tokens, chunk by chunk, state read and written once
+                             (steps with long portions: pgk_seq_linear_attention_chunks, all chunks at once in three passes)
   pgk_seq_linear_finish      output norm (all heads together with a weight, or head by head without), gate, constant factor
 
 and the output projection.  Every constant comes from the `LinearMixerSpec`.  `attend` is the mixer without its two matrix
@@ -31,6 +32,8 @@ from .paged_attention import PagedAttentionMixer
 
 class LinearAttentionMixer:
     queries_per_tile = None              # no attention tiles
+    SEQUENTIAL_CHUNKS = 2                # steps whose longest portion has more chunks take the three-pass form
+    WORKSPACE_FLOATS = 1 << 26           # 256 MB of chunk states at most per segment
 
     def __init__(self, spec: LinearMixerSpec, layer: int, qkvg: "LinearRows | None", o_proj: "LinearRows | None",
                  norm_weight: "GPUArray | None", eps: float, out_mult: float = 1.0):
@@ -49,6 +52,7 @@ class LinearAttentionMixer:
         if norm_weight is not None and norm_weight.size != self.v_cols:
             raise ValueError(f"layer {layer}: the output norm's weight has {norm_weight.size} elements, not {self.v_cols}")
         self.decay = from_numpy(np.asarray(s.decay, np.float32))
+        self.chunk_tokens = int(api.seq_linear_chunk_tokens())
         self.inv_freq = from_numpy(np.asarray(s.rot.inv_freq(), np.float64)) if s.rot is not None else None
 
     @property
@@ -83,9 +87,21 @@ class LinearAttentionMixer:
                             s.rot.dims if s.rot is not None else 0,
                             self.inv_freq.device_ptr if self.inv_freq is not None else None, float(s.k_scale), ctx.pos_ptr, _st())
         seqs_ptr, n_seqs = ctx.seqs()
-        ds = int(api.seq_linear_value_slice(s.heads, s.dim, s.vdim, n_seqs))
-        api.seq_linear_attention(proj_ptr, ld, 0, k_off, v_off, attn_ptr, ldo, state[0].device_ptr, self.decay.device_ptr,
-                                 seqs_ptr, n_seqs, s.heads, s.dim, s.vdim, ds, _st())
+        chunk = self.chunk_tokens
+        n_chunks = -(-ctx.max_rows // chunk)
+        if n_chunks > self.SEQUENTIAL_CHUNKS:
+            # long prompts: every chunk at once (three launches), in segments that bound the workspace
+            per = n_seqs * s.heads * s.dim * s.vdim
+            seg = max(1, min(n_chunks, self.WORKSPACE_FLOATS // per))
+            ws = ctx.workspace(seg * per).device_ptr
+            for c0 in range(0, n_chunks, seg):
+                api.seq_linear_attention_chunks(proj_ptr, ld, 0, k_off, v_off, attn_ptr, ldo, state[0].device_ptr,
+                                                self.decay.device_ptr, seqs_ptr, n_seqs, s.heads, s.dim, s.vdim, c0,
+                                                min(seg, n_chunks - c0), ws, _st())
+        else:
+            ds = int(api.seq_linear_value_slice(s.heads, s.dim, s.vdim, n_seqs))
+            api.seq_linear_attention(proj_ptr, ld, 0, k_off, v_off, attn_ptr, ldo, state[0].device_ptr, self.decay.device_ptr,
+                                     seqs_ptr, n_seqs, s.heads, s.dim, s.vdim, ds, _st())
         gate_act = {"none": 0, "sigmoid": 1, "silu": 2}[s.gate]
         api.seq_linear_finish(attn_ptr, ldo, proj_ptr if gate_act else None, ld, v_off + self.v_cols,
                               self.norm_weight.device_ptr if self.norm_weight is not None else None, T, s.heads, s.vdim,

@@ -52,6 +52,7 @@ class StepContext:
             seqs.append((row, n, slot, pos0))
             row += n
         self.T, self.n_want = row, len(want_rows)
+        self.max_rows = max(n for _, n, _, _ in seqs)          # the longest portion of the step
         self._seqs, self._model = seqs, model
         self.decode_only = all(n == 1 and p0 > 0 for _, n, _, p0 in seqs)
         parts = [np.asarray(toks, np.int32), np.asarray(slots, np.int32), np.asarray(poss, np.int32),

@@ -311,6 +311,8 @@ def random_layered_model(config, dtype: str = "bfloat16", seed: int = 1234, std:
 
     if config.block == "parallel":
         return _random_parallel_model(config, dtype, mat, vec)
+    if config.block == "pre_norm":
+        return _random_pre_norm_model(config, dtype, mat, vec)
     blocks, mixing = [], False
     for i, L in enumerate(config.layers):
         m = L.mixer
@@ -374,3 +376,53 @@ def _random_parallel_model(config, dtype, mat, vec):
         blocks.append(ParallelBlock(norm(), mixer, vec(W, 1.0), mlp, vec(W, 1.0) if mlp is not None else None, side))
     return LayeredCausalModel(config, mat(V, W), blocks, norm(), LinearRows(mat(V, W)), dtype,
                               embed_norm=norm() if config.embed_norm else None)
+
+
+def _random_pre_norm_model(config, dtype, mat, vec):
+    """The pre-norm form of `random_layered_model` (input convolutions, linear-attention / windowed / parallel mixers,
+    squared-ReLU feed-forward): random matrices, norms at identity, small convolution taps, distance numbers and weight
+    biases at fixed values."""
+    from .layers.block import PreNormBlock
+    from .layers.dense_rows import SquaredReluRows
+    from .layers.linear import LinearRows
+    from .layers.linear_attention import LinearAttentionMixer, ParallelMixer
+    from .layers.norm import CausalConvRows, RowNorm
+    from .layers.paged_attention import PagedAttentionMixer
+    from .models.layered import LayeredCausalModel
+    W, V, eps, taps = config.hidden_size, config.vocab_size, config.norm_eps, config.conv_taps
+    mult = vec(W, config.residual_mult)
+
+    def norm():
+        return RowNorm("layernorm_nobias", vec(W, 1.0), None, eps)
+
+    def conv():
+        return CausalConvRows(from_numpy(np.full((W, taps), 0.1, np.float32))) if taps > 0 else None
+
+    def attention(m, layer, fused, out_mult=1.0):
+        dist = (vec(m.heads, 0.5), vec(m.heads, 1.0)) if m.distance_bias == "log" else None
+        return PagedAttentionMixer(m, layer, None if fused else LinearRows(mat(m.proj_cols, W)),
+                                   None if fused else LinearRows(mat(W, m.attn_cols)), None, None, eps, distance=dist,
+                                   weight_bias=vec(m.heads, -4.0) if m.weights == "sigmoid" else None, out_mult=out_mult)
+
+    def linear(m, layer, fused, out_mult=1.0):
+        return LinearAttentionMixer(m, layer, None if fused else LinearRows(mat(m.proj_cols, W)),
+                                    None if fused else LinearRows(mat(W, m.attn_cols)),
+                                    vec(m.attn_cols, 1.0) if m.out_norm == "all" else None, eps, out_mult=out_mult)
+
+    blocks = []
+    for i, L in enumerate(config.layers):
+        m = L.mixer
+        if m.kind == "linear_attention":
+            mixer = linear(m, i, False)
+        elif m.kind == "attention":
+            mixer = attention(m, i, False)
+        else:
+            mixer = ParallelMixer(m, i, LinearRows(mat(m.proj_cols, W)), LinearRows(mat(W, m.attn_cols)),
+                                  attention(m.left, i, True, m.left_scale), linear(m.right, i, True, m.right_scale))
+        mlp = norm2 = conv2 = None
+        if L.mlp is not None:
+            mlp = SquaredReluRows(L.mlp, LinearRows(mat(L.mlp.ff, W)), LinearRows(mat(W, L.mlp.ff)))
+            norm2, conv2 = norm(), conv()
+        blocks.append(PreNormBlock(norm(), conv(), mixer, norm2, conv2, mlp, mult))
+    head = LinearRows(mat(V, W), epilogue=2, scale=config.logit_scale, cap=0.0)
+    return LayeredCausalModel(config, mat(V, W), blocks, norm(), head, dtype)

@@ -39,6 +39,17 @@ TURUTAR_SIZES = {
 }
 
 
+# Rezulorn: pre-norm blocks with input convolutions; a parallel layer (sigmoid-weighted rotary attention over the whole
+# context beside rotary retention), a lightning layer (decayed linear attention, state only) and a windowed attention layer
+# with kept first positions; squared-ReLU feed-forward
+REZULORN_SIZES = {
+    "r-2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=4, lin_heads=16, lin_dim=128, lin_vdim=128,
+                   ff=8192, taps=4, vocab=32768),
+    "r-4096": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, keep=4, lin_heads=32, lin_dim=128, lin_vdim=128,
+                   ff=12288, taps=4, vocab=32768),
+}
+
+
 def peaks(root: str) -> tuple[float, float, str]:
     p = os.path.join(root, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -82,8 +93,46 @@ def dense_twin_config(s: dict):
              "scale": s["dim"] ** -0.5, "softcap": 50.0, "v_mix": False, "vdim": s["dim"]}
     mlp = {"expert": {"ff": s["ff"]}, "kind": "moe", "router": {"experts": 1, "groups": {"count": 1, "keep": 1}, "top": 1}, "shared": None}
     return layered_config_from_json({"architecture": "Dolurax", "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp}
-                                                                            for _ in range(2 * s["times"])],
+                                                                            for _ in range(int(2 * s["times"]))],
                                      "logit_scale": 1.0, "logit_softcap": 0.0, "norm": {"eps": 1e-5}, "vocab": s["vocab"], "width": s["width"]})
+
+
+def rezulorn_config(s: dict):
+    from pygpukit_b200.llm.config import layered_config_from_json
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    H, G, D, Hl, Dl, Dvl = s["heads"], s["kv_heads"], s["dim"], s["lin_heads"], s["lin_dim"], s["lin_vdim"]
+    decay = [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, Hl - 1)) for h in range(Hl)]
+    left = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "rot": {"dims": D, "base": 10000.0, "scaling": {"factor": 4.0}}}
+    right = {"heads": Hl, "dim": Dl, "vdim": Dvl, "decay": decay, "rot": {"dims": Dl, "base": 100000.0}}
+    layers = [{"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 0.75}},
+              {"type": "lightning", "mlp": mlp, "mixer": {"heads": Hl, "dim": Dl, "vdim": Dvl, "decay": decay}},
+              {"type": "attention", "mlp": mlp, "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5,
+                                                           "mask": {"size": s["window"], "keep_first": s["keep"]}}}]
+    return layered_config_from_json({"architecture": "Rezulorn", "layers": layers, "canon": {"taps": s["taps"]}, "norm": {"eps": 1e-6},
+                                     "residual_mult": 0.5, "logit_scale": 1.0, "vocab": s["vocab"], "width": s["width"]})
+
+
+def rezulorn_twin_config(s: dict):
+    """The closest existing model at equal size: three Dolurax layers, attention with the same heads and a chunk of the
+    window's size, one expert of the same feed-forward size (top 1, gated: three matrices to Rezulorn's two)."""
+    return dense_twin_config(dict(s, times=1.5))
+
+
+def rezulorn_bytes_flops(s: dict, T: int, B: int, ctx: int) -> tuple[float, float]:
+    """(bytes a decode step of B tokens touches, FLOPs of a T-token prefill; linear attention counted in its recurrent form)"""
+    W, H, G, D = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    Hl, Dl, Dvl = s["lin_heads"], s["lin_dim"], s["lin_vdim"]
+    att_w = (H * D + 2 * G * D) * W + W * H * D
+    lin_w = (2 * Hl * Dl + 2 * Hl * Dvl) * W + W * Hl * Dvl
+    ff_w = 2 * s["ff"] * W
+    weights = 2 * att_w + 2 * lin_w + 3 * ff_w
+    seen = min(ctx, s["window"] + s["keep"])
+    state = 2 * 4 * Hl * Dl * Dvl                                         # float32, read and written
+    dec = 2 * weights + B * (2 * 2 * G * D * (ctx + seen) + 2 * state) + 2 * s["vocab"] * W
+    win = s["window"]
+    seen_avg = min(T, win) / 2 if T <= win else win * (1 - win / (2 * T))
+    attn_fl = 2 * T * H * (T / 2) * 2 * D + 2 * T * H * seen_avg * 2 * D + 2 * T * Hl * 4 * Dl * Dvl
+    return float(dec), float(2 * T * weights + attn_fl + 2 * s["vocab"] * W)
 
 
 def turutar_bytes_flops(s: dict, T: int, B: int, ctx: int) -> tuple[float, float]:
@@ -257,6 +306,28 @@ def main_turutar(root: str, sizes: list[str], steps: int, warm: int, prompt: int
                                        (1, 8), steps, max(3, warm), hbm, tflops)
         api.device_sync()
         entry["dolurax_dense_twin"] = run_layered(dense_twin_config(s), lambda T, B, ctx: twin_bytes_flops(s, T, B, ctx), s["vocab"],
+                                                  prompt, (1, 8), steps, max(3, warm), hbm, tflops)
+        api.device_sync()
+        res["sizes"][name] = entry
+    return res
+
+
+def main_rezulorn(root: str, sizes: list[str], steps: int, warm: int, prompt: int = 2000) -> dict:
+    """Rezulorn beside a dense Dolurax stack of the same family at equal size: prefill of `prompt` tokens, decode of 1 and 8
+    requests at that context."""
+    from pygpukit_b200._lib import api
+    hbm, tflops, src = peaks(root)
+    res = {"metric": "rezulorn_prefill_decode_tokens_per_s", "data": "synthetic",
+           "dtype": "bf16 matrices and cache, f32 residual / norms / scores / recurrent state",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "prompt": prompt, "steps": steps, "warmup": warm, "sizes": {}}
+    for name in sizes:
+        s = REZULORN_SIZES[name]
+        entry = {"shape": dict(s)}
+        entry["rezulorn"] = run_layered(rezulorn_config(s), lambda T, B, ctx: rezulorn_bytes_flops(s, T, B, ctx), s["vocab"], prompt,
+                                        (1, 8), steps, max(3, warm), hbm, tflops)
+        api.device_sync()
+        twin = dict(s, times=1.5)
+        entry["dolurax_dense_twin"] = run_layered(rezulorn_twin_config(s), lambda T, B, ctx: twin_bytes_flops(twin, T, B, ctx), s["vocab"],
                                                   prompt, (1, 8), steps, max(3, warm), hbm, tflops)
         api.device_sync()
         res["sizes"][name] = entry

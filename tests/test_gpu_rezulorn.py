@@ -159,6 +159,7 @@ class LinearHarness:
         self.pos = {}
         self.cols = 2 * H * D + 2 * H * Dv
         self.slice = None
+        self.segment = 0                                                 # > 0: the three-pass form, this many chunks per call
 
     def run(self, batch):
         """batch: [(slot, q [n, H, D], k, v [n, H, Dv], gate [n, H * Dv])]"""
@@ -176,9 +177,17 @@ class LinearHarness:
         proj, out = f32(rows), gk.zeros((T, H * Dv), gk.float32)
         api.seq_linear_prep(proj.device_ptr, self.cols, T, H, D, Dv, 0, H * D, 2 * H * D, 1 if self.act else 0, self.dims,
                             f64(self.inv_freq).device_ptr if self.dims else None, self.k_scale, i32(pos).device_ptr, None)
-        ds = self.slice or int(api.seq_linear_value_slice(H, D, Dv, len(seqs)))
-        api.seq_linear_attention(proj.device_ptr, self.cols, 0, H * D, 2 * H * D, out.device_ptr, H * Dv, self.state.device_ptr,
-                                 f32(self.decay).device_ptr, i32(seqs).device_ptr, len(seqs), H, D, Dv, ds, None)
+        if self.segment:
+            n_chunks = -(-max(n for _, n, _, _ in seqs) // int(api.seq_linear_chunk_tokens()))
+            ws = keep(gk.zeros((len(seqs) * self.segment * H * D * Dv,), gk.float32))
+            for c0 in range(0, n_chunks, self.segment):
+                api.seq_linear_attention_chunks(proj.device_ptr, self.cols, 0, H * D, 2 * H * D, out.device_ptr, H * Dv,
+                                                self.state.device_ptr, f32(self.decay).device_ptr, i32(seqs).device_ptr, len(seqs),
+                                                H, D, Dv, c0, min(self.segment, n_chunks - c0), ws.device_ptr, None)
+        else:
+            ds = self.slice or int(api.seq_linear_value_slice(H, D, Dv, len(seqs)))
+            api.seq_linear_attention(proj.device_ptr, self.cols, 0, H * D, 2 * H * D, out.device_ptr, H * Dv, self.state.device_ptr,
+                                     f32(self.decay).device_ptr, i32(seqs).device_ptr, len(seqs), H, D, Dv, ds, None)
         api.seq_linear_finish(out.device_ptr, H * Dv, proj.device_ptr, self.cols, 2 * H * D + H * Dv,
                               f32(self.w).device_ptr if self.w is not None else None, T, H, Dv, 1 if self.per_head else 0,
                               self.gate_act, 1e-6, self.mult, None)
@@ -225,6 +234,15 @@ def test_linear_attention_whole_portions_and_single_tokens_agree_with_the_oracle
     h.pos.clear()
     h.slice = 4                                                          # narrow value slices give the same answer
     assert np.abs(h.run([(0, q, k, v, g)])[0] - ref).max() < tol
+    for segment in (1, 2, 8):                                            # all chunks at once, in segments of 1, 2, all
+        h.segment = segment
+        h.pos.clear()
+        assert np.abs(h.run([(0, q, k, v, g)])[0] - ref).max() < tol, segment
+        h.pos.clear()                                                    # a prompt in two portions beside a short sequence
+        first = h.run([(1, q[:40], k[:40], v[:40], g[:40]), (2, q[:3], k[:3], v[:3], g[:3])])
+        rest = h.run([(2, q[3:5], k[3:5], v[3:5], g[3:5]), (1, q[40:], k[40:], v[40:], g[40:])])
+        assert np.abs(np.concatenate([first[0], rest[1]]) - ref).max() < tol, segment
+        assert np.abs(np.concatenate([first[1], rest[0]]) - ref[:5]).max() < tol, segment
 
 
 def test_linear_attention_unequal_sequences_in_one_step_and_a_reused_slot():
@@ -275,6 +293,7 @@ def test_linear_attention_carries_one_early_token_over_hundreds(decoded):
                                                                         for i in range(n0, T)]
                 got = np.concatenate(got)
             else:
+                h.segment = 3                                            # the three-pass form, two segments per portion
                 got = np.concatenate([h.run([(0, q[a:b], k[a:b], v[a:b], g[a:b])])[0] for a, b in cuts_of([100, 130, 100])])
         finally:
             api.seq_linear_finish = api_finish
@@ -471,8 +490,8 @@ def tokens(cfg, n, seed=0):
 
 @pytest.mark.parametrize("name", list(VARIANTS))
 def test_whole_prompt_and_every_layer_match_the_oracle_float32(name):
-    cfg, P, m = make(name)
-    toks = tokens(cfg, 45)
+    cfg, P, m = make(name, tokens_hint=128)
+    toks = tokens(cfg, 75)                                               # long enough for the three-pass linear attention
     ref, layers = R.forward(cfg, P, toks, True)
     seen = []
     m.trace_hook = lambda run, x: seen.append(x)
