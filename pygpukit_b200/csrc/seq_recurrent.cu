@@ -246,12 +246,21 @@ __global__ void __launch_bounds__(256) linear_chunk_scan_kernel(LinChunkArgs a, 
     float* Sg = a.state + ((size_t)sq.z * a.H + h) * per + e;
     float S = (sq.w > 0 || a.c_begin > 0) ? *Sg : 0.f;
     const int cend = min(nchunks, a.c_begin + seg_chunks);
-    for (int c = a.c_begin; c < cend; ++c) {
-        float* u = a.ws + (((size_t)blockIdx.z * seg_chunks + (c - a.c_begin)) * a.H + h) * per + e;
-        const int nc = min(LC, sq.y - c * LC);
-        const float add = *u;
-        *u = S;
-        S = fmaf(S, nc == LC ? dfull : powf(dec, (float)nc), add);
+    const float dlast = powf(dec, (float)(sq.y - (nchunks - 1) * LC));      // the sequence's last chunk may be short
+    float* u0 = a.ws + (((size_t)blockIdx.z * seg_chunks) * a.H + h) * per + e;
+    const size_t step = (size_t)a.H * per;
+    constexpr int B = 8;                                                    // loads in flight per thread
+    for (int c = a.c_begin; c < cend; c += B) {
+        float add[B];
+#pragma unroll
+        for (int i = 0; i < B; ++i) add[i] = c + i < cend ? __ldcs(u0 + (size_t)(c + i - a.c_begin) * step) : 0.f;
+#pragma unroll
+        for (int i = 0; i < B; ++i) {
+            if (c + i < cend) {
+                __stcg(u0 + (size_t)(c + i - a.c_begin) * step, S);
+                S = fmaf(S, c + i == nchunks - 1 ? dlast : dfull, add[i]);
+            }
+        }
     }
     *Sg = S;
 }
