@@ -559,6 +559,9 @@ int pgk_seq_mixer_prep_rot(float* proj, int ld, int tokens, int heads, int kv_he
  * causal_conv_rows: u[t] = h[t] + sum_j weight[:, j] * h at position (pos[t] - taps + 1 + j), weight [width][taps]; inputs of
  * earlier steps come from state [slots][taps - 1][width] (position p in ring row p mod (taps - 1)), positions below 0 are
  * zero.  causal_conv_state: the step's last taps - 1 input rows of every sequence enter the ring (launch it after the rows).
+ * parity != NULL: state is [slots][2][taps - 1][width], two copies of the ring; parity[t] (0 / 1, the same for all rows of a
+ * sequence, flipped by the caller every step) names the copy this step reads, and causal_conv_rows itself writes the other
+ * one (no causal_conv_state launch).
  * linear_prep, on proj rows holding q / k (heads x dim) and v (heads x vdim) at the three offsets: activation 1 = SiLU on
  * all three; the first rot_dims elements of every q and k head rotated as in pgk_seq_mixer_prep_rot; k times k_scale.
  * linear_attention: per head S <- decay[h] S + k v^T, out[t, h] = S^T q, token by token; state [slots][heads][dim][vdim]
@@ -567,7 +570,7 @@ int pgk_seq_mixer_prep_rot(float* proj, int ld, int tokens, int heads, int kv_he
  * linear_finish, in place on out rows: per_head 0: divided by the root mean square over heads x vdim, 1: head by head; times
  * weight [heads x vdim] when given; times sigmoid (gate_act 1) or silu (2) of gate_rows[t, gate_off + i]; times mult. */
 int pgk_causal_conv_rows_f32(const float* h, float* u, const float* weight, float* state, const int32_t* slot,
-                             const int32_t* pos, int rows, int width, int taps, void* stream);
+                             const int32_t* pos, const int32_t* parity, int rows, int width, int taps, void* stream);
 int pgk_causal_conv_state_f32(const float* h, float* state, const int32_t* seqs, int n_seqs, int width, int taps, void* stream);
 int pgk_seq_linear_prep(float* proj, int ld, int tokens, int heads, int dim, int vdim, int q_off, int k_off, int v_off,
                         int activation, int rot_dims, const double* inv_freq, float k_scale, const int32_t* pos, void* stream);

@@ -127,7 +127,7 @@ _SIGS = {
                               i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, vp, f32, i32, vp, vp, i32, vp],
     "pgk_seq_mixer_prep_rot": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp, f32, vp, vp, i32, vp, i32,
                                i32, vp, vp, vp],
-    "pgk_causal_conv_rows_f32": [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
+    "pgk_causal_conv_rows_f32": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
     "pgk_causal_conv_state_f32": [vp, vp, vp, i32, i32, i32, vp],
     "pgk_seq_linear_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp],
     "pgk_seq_linear_attention": [vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],

@@ -5,7 +5,8 @@
 //                      from the rows before it (rows of a sequence are consecutive), older ones from the sequence's state:
 //                      a ring of taps - 1 rows per slot, position p at ring row p mod (taps - 1); positions below 0 are zero.
 //   causal_conv_state  the step's last taps - 1 inputs of every sequence enter the ring (a launch of its own: rows of the
-//                      same launch still read the old ring).
+//                      same launch still read the old ring).  With the ring kept twice per slot (read one copy, write the
+//                      other, the step's parity says which) the rows' launch updates it itself.
 //   linear_prep        per token and head on the fused projection row: activation of q / k / v, rotation of q and k (the
 //                      first rot_dims elements, element i paired with i + rot_dims / 2), k scaled.
 //   linear_attention   S_t = a_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t.  A block owns one (sequence, head, slice of value
@@ -28,23 +29,34 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 // ---------------------------------------------------------------- causal convolution
 struct ConvArgs {
     const float* h; float* u; const float* w; float* state;
-    const int* slot; const int* pos; int W, taps;
+    const int* slot; const int* pos; const int* parity; int T, W, taps;
 };
 
+// parity == NULL: one ring per slot, updated by causal_conv_state_kernel afterwards.  Otherwise the ring is kept twice per
+// slot, [2][taps - 1][W]: the step reads the copy parity[t] of its sequence and this launch writes the other one -- every row
+// among the last taps - 1 of its sequence its own input, the sequence's last row also the entries that stay valid when the
+// step brought fewer than taps - 1 rows -- so that no block reads what another block of the same launch writes.
 __global__ void __launch_bounds__(256) causal_conv_rows_kernel(ConvArgs a) {
     const int t = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
     if (c >= a.W) return;
-    const int p = a.pos[t], s = a.slot[t], ring = a.taps - 1;
+    const int p = a.pos[t], s = a.slot[t], ring = a.taps - 1, W = a.W;
+    const bool twice = a.parity != nullptr;
+    const int par = twice ? (a.parity[t] & 1) : 0;
+    const float* rin = a.state + ((size_t)s * (twice ? 2 : 1) + par) * ring * W;
+    float* rout = a.state + ((size_t)s * 2 + (par ^ 1)) * ring * W;
+    const bool last_row = twice && (t + 1 >= a.T || a.slot[t + 1] != s);
+    const bool tail_row = twice && ring > 0 && (t + ring >= a.T || a.slot[t + ring] != s);
     const float* w = a.w + (size_t)c * a.taps;
-    const float hv = a.h[(size_t)t * a.W + c];
+    const float hv = a.h[(size_t)t * W + c];
     float acc = fmaf(w[a.taps - 1], hv, hv);
     for (int k = 1; k < a.taps && k <= p; ++k) {
-        float v;
-        if (t - k >= 0 && a.slot[t - k] == s) v = a.h[(size_t)(t - k) * a.W + c];
-        else v = a.state[((size_t)s * ring + (p - k) % ring) * a.W + c];
+        const bool instep = t - k >= 0 && a.slot[t - k] == s;
+        const float v = instep ? a.h[(size_t)(t - k) * W + c] : rin[(size_t)((p - k) % ring) * W + c];
         acc = fmaf(w[a.taps - 1 - k], v, acc);
+        if (last_row && k < ring && !instep) rout[(size_t)((p - k) % ring) * W + c] = v;
     }
-    a.u[(size_t)t * a.W + c] = acc;
+    a.u[(size_t)t * W + c] = acc;
+    if (tail_row) rout[(size_t)(p % ring) * W + c] = hv;
 }
 
 // seqs [n][4] = (first row, rows, slot, first position); block x = sequence * ring + i: the i-th last row of the sequence
@@ -412,11 +424,11 @@ __global__ void __launch_bounds__(256) linear_finish_kernel(LinFinishArgs a) {
 extern "C" {
 
 int pgk_causal_conv_rows_f32(const float* h, float* u, const float* weight, float* state, const int32_t* slot,
-                             const int32_t* pos, int rows, int width, int taps, void* stream) {
+                             const int32_t* pos, const int32_t* parity, int rows, int width, int taps, void* stream) {
     PGK_REQUIRE(taps >= 1 && width > 0 && (taps == 1 || state), "causal_conv_rows failed: taps %d, width %d", taps, width);
     PGK_REQUIRE(h != u, "causal_conv_rows failed: the output rows must not be the input rows");
     if (rows <= 0) return 0;
-    ConvArgs a{h, u, weight, state, slot, pos, width, taps};
+    ConvArgs a{h, u, weight, state, slot, pos, taps > 1 ? parity : nullptr, rows, width, taps};
     PGK_CUDA(launch(causal_conv_rows_kernel, dim3(rows, (width + 255) / 256), dim3(256), 0, (cudaStream_t)stream, a));
     return 0;
 }

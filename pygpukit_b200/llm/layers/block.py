@@ -183,20 +183,22 @@ class PreNormBlock:
         h, u = ctx.buf.h, ctx.buf.y
         state = list(ctx.cache.state[cache_index]) if cache_index is not None else []
         rings = {id(c): state.pop(0) for c in self._convs}
-        src = h
-        self.norm1.forward(x.device_ptr, h.device_ptr, T, W)
-        if self.conv1 is not None:
-            self.conv1.forward(ctx, h.device_ptr, u.device_ptr, rings.get(id(self.conv1)))
-            src = u
+        src = self._normed(ctx, self.norm1, self.conv1, rings, x, h, u)
         self.mixer.forward(ctx, src, x, cache_index, out_scale=self.mult.device_ptr, state=state)
         if self.mlp is not None:
-            src = h
-            self.norm2.forward(x.device_ptr, h.device_ptr, T, W)
-            if self.conv2 is not None:
-                self.conv2.forward(ctx, h.device_ptr, u.device_ptr, rings.get(id(self.conv2)))
-                src = u
+            src = self._normed(ctx, self.norm2, self.conv2, rings, x, h, u)
             self.mlp.forward(ctx, src.device_ptr, x.device_ptr, out_scale=self.mult.device_ptr)
         return False
+
+    @staticmethod
+    def _normed(ctx, norm, conv, rings, x: GPUArray, h: GPUArray, u: GPUArray) -> GPUArray:
+        """the sublayer's input: norm(x), or conv(norm(x))"""
+        T, W = ctx.T, x.shape[1]
+        norm.forward(x.device_ptr, h.device_ptr, T, W)
+        if conv is None:
+            return h
+        conv.forward(ctx, h.device_ptr, u.device_ptr, rings.get(id(conv)))
+        return u
 
     @property
     def weight_bytes(self) -> int:

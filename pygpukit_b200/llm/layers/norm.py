@@ -75,16 +75,19 @@ class RowNorm:
 class CausalConvRows:
     """Short causal convolution over time in front of a sublayer of the token-major models: u_t = h_t + sum_j w[:, j]
     h_(t - taps + 1 + j), channel by channel, zeros before the sequence's start.  The last taps - 1 inputs of every sequence
-    are state: a ring of taps - 1 rows per slot in the cache manager (`state_size` float32 elements per slot).  Two launches:
-    the rows, then the ring update (rows of the same launch still read the old ring)."""
+    are state: a ring of taps - 1 rows per slot in the cache manager (`state_size` float32 elements per slot).  With
+    `double_ring` (the default) the ring is kept twice per slot, a step reads one copy and writes the other (the step
+    context's parity), and rows and ring update are ONE launch; without it the ring update is a second launch (rows of the
+    first still read the old ring)."""
 
-    def __init__(self, weight: GPUArray):
+    def __init__(self, weight: GPUArray, double_ring: bool = True):
         self.weight = weight                                  # [width, taps] float32
         self.width, self.taps = weight.shape
+        self.double_ring = bool(double_ring)
 
     @property
     def state_size(self) -> int:
-        return max(0, self.taps - 1) * self.width
+        return max(0, self.taps - 1) * self.width * (2 if self.double_ring else 1)
 
     @property
     def nbytes(self) -> int:
@@ -94,9 +97,9 @@ class CausalConvRows:
         from ..._lib import api
         from ...core.stream import current_stream_handle as _st
         sp = state.device_ptr if state is not None else None
-        api.causal_conv_rows_f32(h_ptr, u_ptr, self.weight.device_ptr, sp, ctx.slot_ptr, ctx.pos_ptr, ctx.T, self.width,
-                                 self.taps, _st())
-        if self.taps > 1:
+        api.causal_conv_rows_f32(h_ptr, u_ptr, self.weight.device_ptr, sp, ctx.slot_ptr, ctx.pos_ptr,
+                                 ctx.parity_ptr if self.double_ring else None, ctx.T, self.width, self.taps, _st())
+        if self.taps > 1 and not self.double_ring:
             seqs_ptr, n_seqs = ctx.seqs()
             api.causal_conv_state_f32(h_ptr, sp, seqs_ptr, n_seqs, self.width, self.taps, _st())
 

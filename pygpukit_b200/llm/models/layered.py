@@ -35,7 +35,7 @@ class StepContext:
 
     def __init__(self, model: "LayeredCausalModel", entries, tile_sizes: set[int], tops: set[int]):
         cache = model.cache
-        toks, slots, poss, want_rows, seqs = [], [], [], [], []
+        toks, slots, poss, want_rows, seqs, pars = [], [], [], [], [], []
         row = 0
         for seq_id, tokens, want in entries:
             n = len(tokens)
@@ -45,6 +45,7 @@ class StepContext:
             toks.extend(int(t) for t in tokens)
             slots.extend([slot] * n)
             poss.extend(range(pos0, pos0 + n))
+            pars.extend([(cache.pool.steps(seq_id) - 1) & 1] * n)      # which copy of double-buffered state the step reads
             for w in want:
                 if not 0 <= int(w) < n:
                     raise ValueError(f"request {seq_id!r}: wanted place {w} outside its {n} tokens")
@@ -83,6 +84,9 @@ class StepContext:
         parts.append(np.asarray(seqs, np.int32).reshape(-1))
         self._seqs_off = cur
         cur += 4 * len(seqs)
+        parts.append(np.asarray(pars, np.int32))
+        par_off = cur
+        cur += self.T
         meta = np.concatenate(parts)
         self.meta = model._meta_buffer(meta.size)
         api.memcpy_h2d(self.meta.device_ptr, meta.ctypes.data, meta.nbytes, _st())
@@ -90,6 +94,7 @@ class StepContext:
         base = self.meta.device_ptr
         self.tok_ptr, self.slot_ptr, self.pos_ptr, self.want_ptr = (base + 4 * off[k] for k in ("tok", "slot", "pos", "want"))
         self._base = base
+        self.parity_ptr = base + 4 * par_off
         cache.sync_table()
         self.cache = cache
         self.buf = model._buffers(self.T)

@@ -38,7 +38,7 @@ class PagePool:
         self._free_slots = list(range(slots))
         heapq.heapify(self._free_pages)
         heapq.heapify(self._free_slots)
-        self._seq: dict = {}            # id -> [slot, [pages], length]
+        self._seq: dict = {}            # id -> [slot, [pages], length, steps that extended it]
         self.table = np.zeros((slots, max_pages_per_seq), np.int32)
         self.dirty = True               # the device copy of `table` is stale
 
@@ -51,6 +51,10 @@ class PagePool:
 
     def slot(self, seq_id) -> int:
         return self._seq[seq_id][0]
+
+    def steps(self, seq_id) -> int:
+        """How many times the sequence has been extended (double-buffered per-sequence state flips on it)."""
+        return self._seq[seq_id][3]
 
     def page_list(self, seq_id) -> list[int]:
         return list(self._seq[seq_id][1])
@@ -94,8 +98,8 @@ class PagePool:
         if ent is None:
             if not self._free_slots:
                 self._grow_slots()
-            ent = self._seq[seq_id] = [heapq.heappop(self._free_slots), [], 0]
-        slot, pages, length = ent
+            ent = self._seq[seq_id] = [heapq.heappop(self._free_slots), [], 0, 0]
+        slot, pages, length, _ = ent
         need = -(-(length + n_tokens) // self.page_size) - len(pages)
         if need > 0:
             if len(pages) + need > self.max_pages:
@@ -108,6 +112,7 @@ class PagePool:
                 pages.append(p)
             self.dirty = True
         ent[2] = length + n_tokens
+        ent[3] += 1
         return slot, length
 
     def truncate(self, seq_id, length: int) -> None:
@@ -122,7 +127,7 @@ class PagePool:
         ent[2] = length
 
     def release(self, seq_id) -> None:
-        slot, pages, _ = self._seq.pop(seq_id)
+        slot, pages, _, _ = self._seq.pop(seq_id)
         for p in pages:
             heapq.heappush(self._free_pages, p)
         heapq.heappush(self._free_slots, slot)

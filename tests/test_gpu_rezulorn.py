@@ -115,7 +115,7 @@ class ConvHarness:
             row += len(r)
         hd, u = f32(h), gk.zeros(h.shape, gk.float32)
         api.causal_conv_rows_f32(hd.device_ptr, u.device_ptr, f32(self.w).device_ptr, self.state.device_ptr, i32(slot).device_ptr,
-                                 i32(pos).device_ptr, len(h), self.W, self.taps, None)
+                                 i32(pos).device_ptr, None, len(h), self.W, self.taps, None)
         api.causal_conv_state_f32(hd.device_ptr, self.state.device_ptr, i32(seqs).device_ptr, len(seqs), self.W, self.taps, None)
         out, at = u.to_numpy(), 0
         res = []
@@ -145,6 +145,60 @@ def test_input_convolution_whole_portions_single_tokens_and_two_sequences(W, tap
                 assert np.abs(out[1] - rb[n:n + 1]).max() < 1e-5
         assert np.abs(np.concatenate(got) - ra).max() < 1e-5
         c.pos.clear()
+
+
+class DoubleRingHarness(ConvHarness):
+    """pgk_causal_conv_rows_f32 with the ring kept twice per slot: rows and ring update in one launch."""
+
+    def __init__(self, W, taps, slots=3):
+        super().__init__(W, taps, slots)
+        self.state = f32(50.0 * np.ones((slots, 2 * max(1, taps - 1) * W)))
+        self.steps = {}
+
+    def run(self, batch):
+        h = np.concatenate([r for _, r in batch])
+        slot = np.concatenate([[s] * len(r) for s, r in batch])
+        pos, par = [], []
+        for s, r in batch:
+            p0 = self.pos.get(s, 0)
+            pos += list(range(p0, p0 + len(r)))
+            par += [self.steps.get(s, 0) & 1] * len(r)
+            self.pos[s] = p0 + len(r)
+            self.steps[s] = self.steps.get(s, 0) + 1
+        u = gk.zeros(h.shape, gk.float32)
+        api.causal_conv_rows_f32(f32(h).device_ptr, u.device_ptr, f32(self.w).device_ptr, self.state.device_ptr, i32(slot).device_ptr,
+                                 i32(pos).device_ptr, i32(par).device_ptr, len(h), self.W, self.taps, None)
+        out, at, res = u.to_numpy(), 0, []
+        for _, r in batch:
+            res.append(out[at:at + len(r)])
+            at += len(r)
+        return res
+
+    def restart(self):
+        self.pos.clear()
+        self.steps.clear()
+
+
+@pytest.mark.parametrize("W,taps", [(40, 4), (300, 2), (33, 5), (16, 1), (3000, 3)])
+def test_input_convolution_with_the_ring_kept_twice(W, taps):
+    rng = np.random.default_rng(taps)
+    a, b = rng.standard_normal((23, W)), rng.standard_normal((9, W))
+    c = DoubleRingHarness(W, taps)
+    ra, rb = R.input_conv(a, c.w), R.input_conv(b, c.w)
+    assert np.abs(c.run([(0, a)])[0] - ra).max() < 1e-5
+    c.restart()                                                          # the same slots again, both ring copies dirty
+    for sizes in ([2] * 4 + [1] * 3 + [5, 7], [1] * 23, [3, 20], [1, 1, 2, 1, 18]):
+        got = []
+        for n, (lo, hi) in enumerate(cuts_of(sizes)):
+            batch = [(0, a[lo:hi])]
+            if n < len(b):                                               # a second sequence decodes beside it, before or after
+                batch.insert(n % 2, (2, b[n:n + 1]))
+            out = c.run(batch)
+            got.append(out[[i for i, (s_, _) in enumerate(batch) if s_ == 0][0]])
+            if n < len(b):
+                assert np.abs(out[[i for i, (s_, _) in enumerate(batch) if s_ == 2][0]] - rb[n:n + 1]).max() < 1e-5
+        assert np.abs(np.concatenate(got) - ra).max() < 1e-5, sizes
+        c.restart()
 
 
 class LinearHarness:
