@@ -643,8 +643,9 @@ def _rezulorn_config(d: dict) -> LayeredConfig:
         elif kind == "attention":
             heads, kv, dim, vdim = heads_of(m, where)
             mask = m.get("mask") or {}
-            mixer = AttentionMixerSpec(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=float(m["scale"]),
-                                       window=int(mask.get("size") or 0), keep_first=int(mask.get("keep_first") or 0),
+            window = int(mask.get("size") or 0)
+            mixer = AttentionMixerSpec(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=float(m["scale"]), window=window,
+                                       keep_first=int(mask.get("keep_first") or 0) if window > 0 else 0,   # no window: all visible
                                        qk_norm=False, out_gate=False, distance_bias="log")
         elif kind == "parallel":
             lm, rm = m["left"], m["right"]
