@@ -589,6 +589,53 @@ int pgk_seq_linear_attention_chunks(const float* proj, int ld, int q_off, int k_
                                     int chunk_begin, int chunks, float* workspace, void* stream);
 int pgk_seq_linear_finish(float* o, int ldo, const float* gate_rows, int ldg, int gate_off, const float* weight, int tokens,
                           int heads, int vdim, int per_head, int gate_act, float eps, float mult, void* stream);
+/* causal_conv_rows with row strides for h and u, without the "h +" (residual 0) and with SiLU on the result (activation 1).
+ * Strided rows need the ring kept twice (parity). */
+int pgk_causal_conv_rows_ex_f32(const float* h, int ldh, float* u, int ldu, const float* weight, float* state, const int32_t* slot,
+                                const int32_t* pos, const int32_t* parity, int rows, int width, int taps, int residual,
+                                int activation, void* stream);
+/* pgk_seq_mixer_prep_rot with projection biases (q_bias [heads x dim], k_bias [kv_heads x dim], v_bias [kv_heads x vdim], any
+ * NULL) added before the rotation, and q_mult [heads] (or NULL), a factor on every query head after rotation and norm. */
+int pgk_seq_mixer_prep_rot_ex(float* proj, int ld, int tokens, int heads, int kv_heads, int dim, int vdim, int q_off, int k_off,
+                              int v_off, int rot_dims, const double* inv_freq, int norm_mode, const float* q_weight,
+                              const float* k_weight, float eps, const float* q_bias, const float* k_bias, const float* v_bias,
+                              const float* q_mult, void* k_cache, void* v_cache, int cache_dtype, const int32_t* table,
+                              int max_pages, int page_size, const int32_t* slot, const int32_t* pos, void* stream);
+/* Pieces with data-dependent gates (seq_gated.cu), float32.
+ * dyt_rows: out[t] (+)= tanh(alpha x[src_rows[t] or t]) * weight + bias (bias may be NULL).
+ * rms_pair_rows: out = mult * (a / rms(a) * weight_a + b / rms(b) * weight_b), rms over the width with eps inside the root.
+ * polynorm_rows, in place on rows of n columns: coef[0] z / rms(z) + coef[1] z^2 / rms(z^2) + coef[2] z^3 / rms(z^3) + coef[3].
+ * moe_route_biased: softmax over `outputs` logits per token; the `top` largest of score + bias (bias may be NULL; ties to the
+ * lower index) -> idx; weights = their scores (divided by their sum when renorm); mat = idx, or -1 for outputs >= real_experts
+ * (experts without matrices); rank / counts as in pgk_moe_route_grouped (both NULL or both given, counts [outputs]).
+ * moe_combine_rows: out[t] = sum_k weights[t, k] * (mat[t, k] < 0 ? self_rows[t] : parts[inv[t, k]])
+ * + sigmoid(gate_rows[t, gate_off]) * shared_rows[t] (no gate_rows: the shared rows as they are; no shared_rows: nothing).
+ * seq_gated_prep, on proj rows: q <- silu(q) (heads x dim at q_off), f <- lower + (1 - lower) sigmoid(f + f_bias) at f_off.
+ * seq_delta_prep: the qk_heads query and key heads of qk_rows to unit length (x / sqrt(sum x^2 + 1e-6)), queries times q_mult;
+ * proj[t, beta_off + h] <- sigmoid(.), proj[t, a_off + h] <- exp(-exp(A_log[h]) softplus(. + dt_bias[h])).
+ * seq_gated_recurrence, per (sequence, head), state [slots][heads][dim][vdim] taken as zero at first position 0:
+ *   delta 0: S <- diag(a_t) S + k_t v_t^T, out = S^T q_t; a rows hold qk_heads x dim decays; k NULL: k_t = 1 - a_t
+ *   delta 1: S <- g S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q; a rows hold g and beta rows beta, one per head
+ * q / k head of value head h: h / (heads / qk_heads). */
+int pgk_dyt_rows_f32(const float* x, const int32_t* src_rows, float alpha, const float* weight, const float* bias, float* out,
+                     int rows, int width, int accumulate, void* stream);
+int pgk_rms_pair_rows_f32(const float* a, const float* weight_a, const float* b, const float* weight_b, float eps, float mult,
+                          float* out, int rows, int width, void* stream);
+int pgk_polynorm_rows_f32(float* z, int ld, const float* coef, float eps, int rows, int n, void* stream);
+int pgk_moe_route_biased(const float* logits, int ld, int tokens, int outputs, int real_experts, int top, const float* bias,
+                         int renorm, int32_t* idx, int32_t* mat, float* weights, int32_t* rank, int32_t* counts, void* stream);
+int pgk_moe_combine_rows_f32(const float* parts, const int32_t* inv, const int32_t* mat, const float* weights, int top,
+                             const float* self_rows, const float* shared_rows, const float* gate_rows, int ldg, int gate_off,
+                             float* out, int rows, int width, void* stream);
+int pgk_seq_gated_prep(float* proj, int ld, int tokens, int heads, int dim, int q_off, int f_off, const float* f_bias,
+                       const float* lower, void* stream);
+int pgk_seq_delta_prep(float* qk_rows, int ldqk, int q_off, int k_off, float* proj, int ld, int beta_off, int a_off,
+                       const float* A_log, const float* dt_bias, int tokens, int heads, int qk_heads, int dim, float q_mult,
+                       void* stream);
+int pgk_seq_gated_recurrence(int delta, const float* q, int ldq, int q_off, const float* k, int ldk, int k_off, const float* a,
+                             int lda, int a_off, const float* beta, int ldb, int b_off, const float* v, int ldv, int v_off,
+                             float* out, int ldo, float* state, const int32_t* seqs, int n_seqs, int heads, int qk_heads, int dim,
+                             int vdim, void* stream);
 /* mixer_prep for layers whose q / k norm runs over the WHOLE projection: per token, q <- (q + q_bias) / rms(all heads x dim
  * of q) * (weight_offset + q_weight) in place (proj[t, 0 ..]), k the same from proj[t, k_off ..] with k_weight into the K
  * pages; the V pages receive k + k_bias as projected (before the norm).  Biases may be NULL; weights are [heads x dim] and

@@ -141,6 +141,19 @@ _SIGS = {
     "pgk_embed_norm_rows_f32": [vp, i32, vp, vp, f32, f32, vp, vp, i32, i32, i32, vp],
     "pgk_gemm_seq_f32": [vp, i32, C.c_longlong, vp, i32, C.c_longlong, vp, i32, C.c_longlong, i32, i32, i32, i32, i32, f32, f32,
                          vp, vp, i32, vp, i32, i32, i32, vp],
+    "pgk_causal_conv_rows_ex_f32": [vp, i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "pgk_seq_mixer_prep_rot_ex": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp,
+                                  i32, vp, i32, i32, vp, vp, vp],
+    # pieces with data-dependent gates (seq_gated.cu)
+    "pgk_dyt_rows_f32": [vp, vp, f32, vp, vp, vp, i32, i32, i32, vp],
+    "pgk_rms_pair_rows_f32": [vp, vp, vp, vp, f32, f32, vp, i32, i32, vp],
+    "pgk_polynorm_rows_f32": [vp, i32, vp, f32, i32, i32, vp],
+    "pgk_moe_route_biased": [vp, i32, i32, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, vp],
+    "pgk_moe_combine_rows_f32": [vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, vp, i32, i32, vp],
+    "pgk_seq_gated_prep": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp],
+    "pgk_seq_delta_prep": [vp, i32, i32, i32, vp, i32, i32, i32, vp, vp, i32, i32, i32, i32, f32, vp],
+    "pgk_seq_gated_recurrence": [i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, vp, i32, vp, vp, i32,
+                                 i32, i32, i32, i32, vp],
     "pgk_seq_mixer_prep": [vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, i32, f32, vp, vp, vp, i32, vp, i32, i32, vp, vp, vp],
     "pgk_seq_attention": [vp, i32, i32, i32, vp, i32, vp, vp, i32, vp, i32, i32, vp, i32, vp, i32, i32, i32, i32, i32, f32,
                           f32, i32, i32, vp, vp, i32, vp],

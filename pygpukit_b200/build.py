@@ -52,13 +52,15 @@ SOURCES = {
     "seq_layers.cu": [],
     "seq_latent.cu": [],
     "seq_recurrent.cu": [],
+    "seq_gated.cu": [],
 }
 
 # groups of sources that link on their own (runtime.cu is in every library)
 COMPONENTS = {
     "core": ["runtime.cu"],
     # token-major float32-activation models on the paged cache (llm/models/layered.py)
-    "seq": ["runtime.cu", "seq_gemm.cu", "seq_attention.cu", "seq_layers.cu", "seq_latent.cu", "seq_recurrent.cu"],
+    "seq": ["runtime.cu", "seq_gemm.cu", "seq_attention.cu", "seq_layers.cu", "seq_latent.cu", "seq_recurrent.cu",
+            "seq_gated.cu"],
 }
 
 

@@ -83,6 +83,8 @@ struct PrepRotArgs {
     const float* qw; const float* kw; float eps;
     void* kc; void* vc; const int* table; int max_pages, PS;
     const int* slot; const int* pos;
+    const float* qb; const float* kb; const float* vb;      // projection biases [H x D], [G x D], [G x Dv] or NULL
+    const float* q_mult;                                     // [H] factor on every query head (a per-head temperature) or NULL
 };
 
 // units: H query heads (rotated and normalised in place), G key heads and G value heads (into the cache); a warp each.
@@ -99,24 +101,31 @@ __global__ void __launch_bounds__(128) mixer_prep_rot_kernel(PrepRotArgs a) {
         const int g = u - a.H - a.G;
         const float* v = row + a.v_off + (size_t)g * a.Dv;
         TC* dst = (TC*)a.vc + (((size_t)page * a.G + g) * a.PS + r) * a.Dv;
-        for (int d = lane; d < a.Dv; d += 32) cstore<TC>(dst + d, v[d]);
+        const float* vb = a.vb ? a.vb + (size_t)g * a.Dv : nullptr;
+        for (int d = lane; d < a.Dv; d += 32) cstore<TC>(dst + d, v[d] + (vb ? vb[d] : 0.f));
         return;
     }
     const bool is_k = u >= a.H;
     const int g = u - a.H;
     float* x = row + (is_k ? a.k_off + (size_t)g * a.D : a.q_off + (size_t)u * a.D);
-    if (!is_k && a.rot_dims == 0 && a.norm == 0) return;           // the query stays as projected
+    const float* bias = is_k ? (a.kb ? a.kb + (size_t)g * a.D : nullptr) : (a.qb ? a.qb + (size_t)u * a.D : nullptr);
+    const float qm = (!is_k && a.q_mult) ? a.q_mult[u] : 1.f;
+    if (!is_k && a.rot_dims == 0 && a.norm == 0 && !bias && !a.q_mult) return;      // the query stays as projected
     const int half = a.rot_dims / 2;
     float ss = 0.f;
     for (int i = lane; i < half; i += 32) {
         float sn, cs;
         rope_angle_sincos(pos, a.inv_freq[i], sn, cs);
-        const float p0 = x[i], p1 = x[i + half];
+        const float p0 = x[i] + (bias ? bias[i] : 0.f), p1 = x[i + half] + (bias ? bias[i + half] : 0.f);
         const float r0 = p0 * cs - p1 * sn, r1 = p1 * cs + p0 * sn;
         x[i] = r0; x[i + half] = r1;
         ss = fmaf(r0, r0, fmaf(r1, r1, ss));
     }
-    for (int d = 2 * half + lane; d < a.D; d += 32) ss = fmaf(x[d], x[d], ss);
+    for (int d = 2 * half + lane; d < a.D; d += 32) {
+        const float v = x[d] + (bias ? bias[d] : 0.f);
+        if (bias) x[d] = v;
+        ss = fmaf(v, v, ss);
+    }
     __syncwarp();
     float inv = 1.f;
     if (a.norm) inv = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
@@ -124,8 +133,8 @@ __global__ void __launch_bounds__(128) mixer_prep_rot_kernel(PrepRotArgs a) {
     if (is_k) {
         TC* dst = (TC*)a.kc + (((size_t)page * a.G + g) * a.PS + r) * a.D;
         for (int d = lane; d < a.D; d += 32) cstore<TC>(dst + d, x[d] * inv * (w ? w[d] : 1.f));
-    } else if (a.norm) {
-        for (int d = lane; d < a.D; d += 32) x[d] = x[d] * inv * (w ? w[d] : 1.f);
+    } else if (a.norm || a.q_mult) {
+        for (int d = lane; d < a.D; d += 32) x[d] = x[d] * inv * (w ? w[d] : 1.f) * qm;
     }
 }
 
@@ -930,6 +939,17 @@ int pgk_seq_mixer_prep_rot(float* proj, int ld, int tokens, int heads, int kv_he
                            int v_off, int rot_dims, const double* inv_freq, int norm_mode, const float* q_weight,
                            const float* k_weight, float eps, void* k_cache, void* v_cache, int cache_dtype, const int32_t* table,
                            int max_pages, int page_size, const int32_t* slot, const int32_t* pos, void* stream) {
+    return pgk_seq_mixer_prep_rot_ex(proj, ld, tokens, heads, kv_heads, dim, vdim, q_off, k_off, v_off, rot_dims, inv_freq, norm_mode,
+                                     q_weight, k_weight, eps, nullptr, nullptr, nullptr, nullptr, k_cache, v_cache, cache_dtype, table,
+                                     max_pages, page_size, slot, pos, stream);
+}
+
+// ---- the same with projection biases on q, k and v and a factor on every query head
+int pgk_seq_mixer_prep_rot_ex(float* proj, int ld, int tokens, int heads, int kv_heads, int dim, int vdim, int q_off, int k_off,
+                              int v_off, int rot_dims, const double* inv_freq, int norm_mode, const float* q_weight,
+                              const float* k_weight, float eps, const float* q_bias, const float* k_bias, const float* v_bias,
+                              const float* q_mult, void* k_cache, void* v_cache, int cache_dtype, const int32_t* table,
+                              int max_pages, int page_size, const int32_t* slot, const int32_t* pos, void* stream) {
     PGK_REQUIRE(cache_dtype == 0 || cache_dtype == 2, "seq_mixer_prep_rot failed: the cache is float32 (0) or bfloat16 (2), got %d", cache_dtype);
     PGK_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "seq_mixer_prep_rot failed: invalid head layout");
     PGK_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || inv_freq),
@@ -937,7 +957,7 @@ int pgk_seq_mixer_prep_rot(float* proj, int ld, int tokens, int heads, int kv_he
     PGK_REQUIRE(norm_mode >= 0 && norm_mode <= 2 && (norm_mode != 2 || (q_weight && k_weight)), "seq_mixer_prep_rot failed: norm mode %d", norm_mode);
     if (tokens <= 0) return 0;
     PrepRotArgs a{proj, ld, heads, kv_heads, dim, vdim, q_off, k_off, v_off, rot_dims, inv_freq, norm_mode, q_weight, k_weight, eps,
-                  k_cache, v_cache, table, max_pages, page_size, slot, pos};
+                  k_cache, v_cache, table, max_pages, page_size, slot, pos, q_bias, k_bias, v_bias, q_mult};
     const dim3 grid(tokens, (heads + 2 * kv_heads + 3) / 4);
     if (cache_dtype == 2) PGK_CUDA(launch(mixer_prep_rot_kernel<uint16_t>, grid, dim3(128), 0, (cudaStream_t)stream, a));
     else PGK_CUDA(launch(mixer_prep_rot_kernel<float>, grid, dim3(128), 0, (cudaStream_t)stream, a));

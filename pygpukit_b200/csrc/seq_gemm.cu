@@ -304,6 +304,7 @@ __global__ void __launch_bounds__(FEW_MAX_WARPS * 32) gemm_few_rows_kernel(GemmA
     const int r0 = blockIdx.y * rows_per_block;
     const int nr = min(rows_per_block, a.M - r0);
     const int grp = a.row_group ? a.row_group[r0] : (int)blockIdx.z;
+    if (grp < 0) return;                                        // a row without a matrix (its output is formed elsewhere)
     a.A += (size_t)blockIdx.z * a.a_z;
     a.C += (size_t)blockIdx.z * a.c_z;
     const TW* W = (const TW*)a.W + (size_t)grp * a.w_stride;

@@ -30,6 +30,8 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 struct ConvArgs {
     const float* h; float* u; const float* w; float* state;
     const int* slot; const int* pos; const int* parity; int T, W, taps;
+    int ldh, ldu;                        // row strides of h and u (W when the rows are dense)
+    int residual, act;                   // residual 1: u = h + conv(h), 0: u = conv(h); act 1: silu on the result
 };
 
 // parity == NULL: one ring per slot, updated by causal_conv_state_kernel afterwards.  Otherwise the ring is kept twice per
@@ -47,15 +49,15 @@ __global__ void __launch_bounds__(256) causal_conv_rows_kernel(ConvArgs a) {
     const bool last_row = twice && (t + 1 >= a.T || a.slot[t + 1] != s);
     const bool tail_row = twice && ring > 0 && (t + ring >= a.T || a.slot[t + ring] != s);
     const float* w = a.w + (size_t)c * a.taps;
-    const float hv = a.h[(size_t)t * W + c];
-    float acc = fmaf(w[a.taps - 1], hv, hv);
+    const float hv = a.h[(size_t)t * a.ldh + c];
+    float acc = fmaf(w[a.taps - 1], hv, a.residual ? hv : 0.f);
     for (int k = 1; k < a.taps && k <= p; ++k) {
         const bool instep = t - k >= 0 && a.slot[t - k] == s;
-        const float v = instep ? a.h[(size_t)(t - k) * W + c] : rin[(size_t)((p - k) % ring) * W + c];
+        const float v = instep ? a.h[(size_t)(t - k) * a.ldh + c] : rin[(size_t)((p - k) % ring) * W + c];
         acc = fmaf(w[a.taps - 1 - k], v, acc);
         if (last_row && k < ring && !instep) rout[(size_t)((p - k) % ring) * W + c] = v;
     }
-    a.u[(size_t)t * W + c] = acc;
+    a.u[(size_t)t * a.ldu + c] = a.act ? silu_f(acc) : acc;
     if (tail_row) rout[(size_t)(p % ring) * W + c] = hv;
 }
 
@@ -423,14 +425,22 @@ __global__ void __launch_bounds__(256) linear_finish_kernel(LinFinishArgs a) {
 
 extern "C" {
 
-int pgk_causal_conv_rows_f32(const float* h, float* u, const float* weight, float* state, const int32_t* slot,
-                             const int32_t* pos, const int32_t* parity, int rows, int width, int taps, void* stream) {
+int pgk_causal_conv_rows_ex_f32(const float* h, int ldh, float* u, int ldu, const float* weight, float* state, const int32_t* slot,
+                                const int32_t* pos, const int32_t* parity, int rows, int width, int taps, int residual,
+                                int activation, void* stream) {
     PGK_REQUIRE(taps >= 1 && width > 0 && (taps == 1 || state), "causal_conv_rows failed: taps %d, width %d", taps, width);
-    PGK_REQUIRE(h != u, "causal_conv_rows failed: the output rows must not be the input rows");
+    PGK_REQUIRE(h != u && ldh >= width && ldu >= width, "causal_conv_rows failed: the output rows must not be the input rows");
+    PGK_REQUIRE(taps == 1 || parity || (ldh == width), "causal_conv_rows failed: strided rows need the ring kept twice");
     if (rows <= 0) return 0;
-    ConvArgs a{h, u, weight, state, slot, pos, taps > 1 ? parity : nullptr, rows, width, taps};
+    ConvArgs a{h, u, weight, state, slot, pos, taps > 1 ? parity : nullptr, rows, width, taps, ldh, ldu, residual ? 1 : 0,
+               activation ? 1 : 0};
     PGK_CUDA(launch(causal_conv_rows_kernel, dim3(rows, (width + 255) / 256), dim3(256), 0, (cudaStream_t)stream, a));
     return 0;
+}
+
+int pgk_causal_conv_rows_f32(const float* h, float* u, const float* weight, float* state, const int32_t* slot,
+                             const int32_t* pos, const int32_t* parity, int rows, int width, int taps, void* stream) {
+    return pgk_causal_conv_rows_ex_f32(h, width, u, width, weight, state, slot, pos, parity, rows, width, taps, 1, 0, stream);
 }
 
 int pgk_causal_conv_state_f32(const float* h, float* state, const int32_t* seqs, int n_seqs, int width, int taps, void* stream) {

@@ -90,9 +90,12 @@ class RowBuffers:
         W = config.hidden_size
         proj = attn = gv = top = ff = sff = experts = 1
         q_up = q_abs = lat = hout = 1
+        conv, second = 0, False
         for L in config.layers:
             m = L.mixer
             proj = max(proj, m.proj_cols)
+            conv = max(conv, getattr(m, "conv_cols", 0))
+            second = second or getattr(m, "join", "sum") == "rms_mean" or bool(getattr(L.mlp, "shared_gate", False))
             if m.kind == "latent_attention":
                 q_up = max(q_up, m.heads * (m.dim + m.rot_dim))
                 q_abs = max(q_abs, m.heads * (m.kv_rank + m.rot_dim))
@@ -105,11 +108,14 @@ class RowBuffers:
                 sff = max(sff, L.mlp.ff)
             elif L.mlp is not None:
                 top, ff, sff = max(top, L.mlp.top), max(ff, L.mlp.ff), max(sff, L.mlp.shared_ff)
-                experts = max(experts, L.mlp.experts)
+                experts = max(experts, getattr(L.mlp, "routes", L.mlp.experts) + 1)
         R = self.rows = max(8, int(rows))
         self.x = GPUArray((R, W), float32)
         self.y = GPUArray((R, W), float32)
-        normed = getattr(config, "block", "post_norm") in ("parallel", "pre_norm")
+        normed = getattr(config, "block", "post_norm") in ("parallel", "pre_norm", "sandwich")
+        self.y2 = GPUArray((R, W), float32) if second else None             # a second branch's rows
+        self.conv = GPUArray((R, conv), float32) if conv else None          # a mixer's convolved columns
+        self.moe_mat = GPUArray((R * top,), int32)                          # matrix of every (token, slot) row, -1: none
         self.h = GPUArray((R, W), float32) if normed else None                          # the block's normed rows
         self.x0 = GPUArray((R, W), float32) if getattr(config, "loop_times", 1) > 1 else None   # embedding output
         self.side = GPUArray((R, max(1, getattr(config, "side_dim", 0))), float32)

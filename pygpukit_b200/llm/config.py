@@ -247,7 +247,9 @@ class AttentionMixerSpec:
     `distance_bias` "slopes": the fixed per-head slopes above (True means the same); "log": r1_h ln(1 + r2_h (i - j)) with two
     learned numbers per head.  `rot`: rotary positions on q and k (a RotarySpec).  `norm_scope` "head" with
     `norm_weight` False divides q and k by their root mean square and multiplies by nothing.  `weights` "softmax", or
-    "sigmoid": the weight of a visible key is sigmoid(score + b_h) with a learned number per head, not normalised."""
+    "sigmoid": the weight of a visible key is sigmoid(score + b_h) with a learned number per head, not normalised.
+    `qkv_bias`: the q, k and v projections have biases (added before the rotation).  `head_temp`: the score is also
+    multiplied by a learned number per head."""
     heads: int
     kv_heads: int
     dim: int
@@ -269,6 +271,8 @@ class AttentionMixerSpec:
     rot: "RotarySpec | None" = None
     norm_weight: bool = True
     weights: str = "softmax"
+    qkv_bias: bool = False
+    head_temp: bool = False
 
     kind = "attention"
 
@@ -352,13 +356,91 @@ class LinearMixerSpec:
 
 
 @dataclass(frozen=True)
+class GatedLinearMixerSpec:
+    """Linear attention whose forget gate also decides what is written, with a float32 state per sequence:
+    S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t, per head; f_t = low + (1 - low) sigmoid(W_f h + b_f) per head
+    and channel with a learned lower bound, q = silu(W_q h); there is no key.  Every head's output is divided by its root
+    mean square and multiplied by a weight vector shared by the heads."""
+    heads: int
+    dim: int
+    vdim: int
+
+    kind = "gated_linear_attention"
+    kv_heads = 0
+    chunk = 0
+    window = 0
+    keep_first = 0
+
+    @property
+    def proj_cols(self) -> int:
+        """columns of the fused projection [q | f | v]"""
+        return 2 * self.heads * self.dim + self.heads * self.vdim
+
+    @property
+    def attn_cols(self) -> int:
+        return self.heads * self.vdim
+
+    def cache_shape(self) -> tuple[int, int, int]:
+        return (0, 0, 0)                 # no cache pages
+
+    @property
+    def state_shapes(self) -> tuple:
+        return (self.heads * self.dim * self.vdim,)
+
+
+@dataclass(frozen=True)
+class DeltaMixerSpec:
+    """Gated delta rule with a float32 state per sequence: per head S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  q and k have `qk_heads` heads of size `dim` (value head h reads head h // (heads / qk_heads)), v `heads` heads
+    of size `vdim`; each passes a causal convolution over `conv_taps` positions per channel and SiLU; q and k are unit
+    vectors (q times dim^-1/2); beta = sigmoid(W_b h), g = exp(-exp(A_log) softplus(W_a h + dt_bias)).  Every head's output
+    is divided by its root mean square, multiplied by a weight vector shared by the heads and by silu of a gate projection.
+    The last conv_taps - 1 inputs of the convolution are per-sequence state too (kept twice, see `CausalConvRows`)."""
+    heads: int
+    qk_heads: int
+    dim: int
+    vdim: int
+    conv_taps: int
+
+    kind = "delta_rule"
+    kv_heads = 0
+    chunk = 0
+    window = 0
+    keep_first = 0
+
+    @property
+    def conv_cols(self) -> int:
+        """channels of the convolution: [q | k | v]"""
+        return 2 * self.qk_heads * self.dim + self.heads * self.vdim
+
+    @property
+    def proj_cols(self) -> int:
+        """columns of the fused projection [q | k | v | gate | beta | a]"""
+        return self.conv_cols + self.heads * self.vdim + 2 * self.heads
+
+    @property
+    def attn_cols(self) -> int:
+        return self.heads * self.vdim
+
+    def cache_shape(self) -> tuple[int, int, int]:
+        return (0, 0, 0)                 # no cache pages
+
+    @property
+    def state_shapes(self) -> tuple:
+        return (self.heads * self.dim * self.vdim, 2 * max(0, self.conv_taps - 1) * self.conv_cols)
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec:
-    """Two mixers side by side on the same input: left_scale * left + right_scale * right (an attention mixer with cache
-    pages and a linear-attention mixer with a state)."""
+    """Two mixers side by side on the same input (an attention mixer with cache pages and a mixer with a state).  `join`
+    "sum": left_scale * left + right_scale * right, one output projection over both sides' heads; "rms_mean": each side has
+    its own output projection, whose result is divided by its root mean square over the width and multiplied by a weight
+    vector, and the result is left_scale * left + right_scale * right of those (1/2 each for the mean)."""
     left: AttentionMixerSpec
-    right: LinearMixerSpec
+    right: "LinearMixerSpec | GatedLinearMixerSpec"
     left_scale: float = 1.0
     right_scale: float = 1.0
+    join: str = "sum"
 
     kind = "parallel"
     chunk = 0
@@ -448,7 +530,8 @@ class LatentMixerSpec:
 class DenseSpec:
     """Gated dense feed-forward: g = W_gate h, u = W_up h, output W_down act(g, u).  activation "silu": silu(g) u;
     "clamped_swish": g <- min(g, limit), u <- clamp(u, -limit, limit), g sigmoid(alpha g) (u + 1).  "relu2" has no gate:
-    W_down max(W_up h, 0)^2."""
+    W_down max(W_up h, 0)^2.  "polynorm" has no gate either: W_down (a N(z) + b N(z^2) + c N(z^3) + e) with z = W_up h,
+    powers element by element, N = division by the root mean square over the ff values, and four learned numbers."""
     ff: int
     activation: str = "silu"
     limit: float = 0.0
@@ -462,21 +545,34 @@ class DenseSpec:
 
 @dataclass(frozen=True)
 class MoESpec:
-    """Routed experts (gate/up/down, SiLU) + optional shared expert.  Router: softmax over all experts, the `top`
-    best among the members of the `group_keep` best of `group_count` groups of neighbours, weights renormalised."""
+    """Routed experts (gate/up/down, SiLU) + optional shared expert.  Router "grouped": softmax over all experts, the `top`
+    best among the members of the `group_keep` best of `group_count` groups of neighbours, weights renormalised.  Router
+    "biased": softmax over experts + identity router outputs, the `top` largest of score + a stored correction are chosen,
+    the weights are the scores themselves (`renorm` False) -- the last `identity` outputs stand for experts that return
+    their input and have no matrices; `shared_gate`: the shared expert's output is multiplied by sigmoid of one more
+    projection, a number per token."""
     experts: int
     top: int
     ff: int
     group_count: int = 1
     group_keep: int = 1
     shared_ff: int = 0
+    router: str = "grouped"
+    identity: int = 0
+    renorm: bool = True
+    shared_gate: bool = False
 
     kind = "moe"
+
+    @property
+    def routes(self) -> int:
+        """router outputs"""
+        return self.experts + self.identity
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    mixer: "AttentionMixerSpec | LatentMixerSpec | LinearMixerSpec | ParallelMixerSpec"
+    mixer: "AttentionMixerSpec | LatentMixerSpec | LinearMixerSpec | GatedLinearMixerSpec | DeltaMixerSpec | ParallelMixerSpec"
     mlp: "MoESpec | DenseSpec | None"
 
 
@@ -492,9 +588,12 @@ class LayeredConfig:
     logit_scale: float = 1.0
     logit_softcap: float = 0.0
     # block form: "post_norm" x += LN(sublayer(x)) twice; "parallel" h = norm(x), x += s1 mixer(h) + s2 ff(h);
-    # "pre_norm" x += m mixer(c1(norm1(x))), x += m ff(c2(norm2(x))) with m = residual_mult and c the input convolution
+    # "pre_norm" x += m mixer(c1(norm1(x))), x += m ff(c2(norm2(x))) with m = residual_mult and c the input convolution;
+    # "sandwich" x += norm1b(mixer(norm1(x))), x += norm2b(ff(norm2(x)))
     block: str = "post_norm"
-    norm: str = "layernorm"            # "layernorm" (weight + bias), "layernorm_nobias" or "rmsnorm_1p" (x / rms * (1 + w))
+    # "layernorm" (weight + bias), "layernorm_nobias", "rmsnorm_1p" (x / rms * (1 + w)) or "dyt" (tanh(alpha x) * w + b)
+    norm: str = "layernorm"
+    tied_head: bool = False            # the logits are products with the embedding table
     residual_mult: float = 1.0         # pre_norm blocks: factor on every sublayer's result before it joins the residual
     conv_taps: int = 0                 # > 0: h <- h + causal convolution over `conv_taps` positions in front of every sublayer
     embed_norm: bool = False           # the model's norm on the embedding output
@@ -676,8 +775,64 @@ def _rezulorn_config(d: dict) -> LayeredConfig:
                          conv_taps=taps)
 
 
+def _sumitar_config(d: dict) -> LayeredConfig:
+    """Sumitar: sandwich blocks (a dynamic-tanh norm before and after every sublayer) of two mixers -- "parallel" (sliding-window
+    rotary softmax attention with q / k / v biases and a per-head temperature beside a gated linear recurrence without keys,
+    each side RMS-normed over the width, the mean of the two) and "delta" (gated delta rule behind short convolutions) -- with a
+    PolyNorm feed-forward or a mixture of experts whose router has a choice bias, experts without matrices and a gated shared
+    expert; the logits are products with the embedding table.  What the design fixes is set here; sizes and constants come
+    from the file."""
+
+    def sizes(m, where, kv_key="kv_heads"):
+        heads, dim = int(m["heads"]), int(m["dim"])
+        kv = int(m.get(kv_key) or heads)
+        if heads < 1 or dim < 1 or kv < 1 or heads % kv:
+            raise ValueError(f"{where}: {heads} heads over {kv} key/value heads")
+        return heads, kv, dim, int(m.get("vdim") or dim)
+
+    layers = []
+    for i, L in enumerate(d["layers"]):
+        m, kind, where = L["mixer"], L.get("type"), f"Sumitar: layer {i}"
+        if kind == "parallel":
+            lm, rm = m["left"], m["right"]
+            heads, kv, dim, vdim = sizes(lm, where + " (left)")
+            left = AttentionMixerSpec(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=float(lm["scale"]),
+                                      window=int((lm.get("mask") or {}).get("size") or 0), qk_norm=False, out_gate=False,
+                                      distance_bias=False, rot=_rotary(lm.get("rot"), dim, where + " (left)"), qkv_bias=True,
+                                      head_temp=True)
+            heads, _, dim, vdim = sizes(rm, where + " (right)")
+            mixer = ParallelMixerSpec(left, GatedLinearMixerSpec(heads=heads, dim=dim, vdim=vdim), 0.5, 0.5, join="rms_mean")
+        elif kind == "delta":
+            heads, qk, dim, vdim = sizes(m, where)
+            taps = int(m.get("conv") or 1)
+            if taps < 1 or dim > 256:
+                raise ValueError(f"{where}: {taps} convolution taps, heads of {dim}")
+            mixer = DeltaMixerSpec(heads=heads, qk_heads=qk, dim=dim, vdim=vdim, conv_taps=taps)
+        else:
+            raise ValueError(f"{where} has unknown type {kind!r}")
+        mlp = None
+        f = L.get("mlp")
+        if f:
+            if f.get("kind") == "dense":
+                mlp = DenseSpec(ff=int(f["ff"]), activation="polynorm")
+            elif f.get("kind") == "moe":
+                r = f["router"]
+                sh = f.get("shared") or {}
+                mlp = MoESpec(experts=int(r["experts"]), top=int(r["top"]), ff=int(f["expert"]["ff"]),
+                              shared_ff=int(sh.get("ff") or 0), router="biased", identity=int(r.get("identity") or 0),
+                              renorm=False, shared_gate=bool(sh.get("ff")))
+                if mlp.experts < 0 or mlp.identity < 0 or not 1 <= mlp.top <= mlp.routes:
+                    raise ValueError(f"{where}: top {mlp.top} of {mlp.experts} + {mlp.identity} experts")
+            else:
+                raise ValueError(f"{where} has unknown feed-forward kind {f.get('kind')!r}")
+        layers.append(LayerSpec(mixer, mlp))
+    return LayeredConfig(architecture="Sumitar", vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), layers=layers,
+                         norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)), block="sandwich", norm="dyt", tied_head=True)
+
+
 # config.json "architecture" -> parser (the model registry of the layered families)
-LAYERED_ARCHITECTURES = {"dolurax": _dolurax_config, "turutar": _turutar_config, "rezulorn": _rezulorn_config}
+LAYERED_ARCHITECTURES = {"dolurax": _dolurax_config, "turutar": _turutar_config, "rezulorn": _rezulorn_config,
+                         "sumitar": _sumitar_config}
 
 
 def layered_config_from_json(d: dict) -> LayeredConfig | None:
@@ -688,5 +843,5 @@ def layered_config_from_json(d: dict) -> LayeredConfig | None:
 
 __all__ = ["ModelSpec", "TransformerConfig", "GPT2Config", "LlamaConfig", "Qwen3Config", "GPT2_SPEC", "LLAMA_SPEC",
            "QWEN2_SPEC", "QWEN3_SPEC", "QWEN3_MOE_SPEC", "MIXTRAL_SPEC", "MODEL_SPECS", "detect_model_spec",
-           "named_config", "AttentionMixerSpec", "LatentMixerSpec", "RotarySpec", "LinearMixerSpec", "ParallelMixerSpec", "DenseSpec", "MoESpec", "LayerSpec", "LayeredConfig",
+           "named_config", "AttentionMixerSpec", "LatentMixerSpec", "RotarySpec", "LinearMixerSpec", "GatedLinearMixerSpec", "DeltaMixerSpec", "ParallelMixerSpec", "DenseSpec", "MoESpec", "LayerSpec", "LayeredConfig",
            "LAYERED_ARCHITECTURES", "layered_config_from_json"]

@@ -208,4 +208,45 @@ class PreNormBlock:
         return n
 
 
-__all__ = ["TransformerBlock", "PostNormBlock", "ParallelBlock", "PreNormBlock"]
+class SandwichBlock:
+    """Block of the token-major models with a norm before AND after each sublayer: x += norm1b(mixer(norm1(x))), then
+    x += norm2b(ff(norm2(x))).  The norms are `RowNorm`s of any kind; the one behind a sublayer adds its result to the residual
+    stream in its own launch.  The feed-forward is any layer with `forward_rows(ctx, rows, out)`.  Per-sequence state of the
+    block in the cache manager: whatever the mixer keeps."""
+
+    def __init__(self, norm1, mixer, norm1b, norm2=None, mlp=None, norm2b=None):
+        self.norm1, self.mixer, self.norm1b, self.norm2, self.mlp, self.norm2b = norm1, mixer, norm1b, norm2, mlp, norm2b
+        if (mlp is None) != (norm2 is None) or (mlp is None) != (norm2b is None):
+            raise ValueError("SandwichBlock: a feed-forward comes with both of its norms")
+
+    norm = None                          # the block's norms are not fused with the block before
+
+    @property
+    def state_shapes(self) -> tuple:
+        return tuple(self.mixer.spec.state_shapes)
+
+    def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None, normed: bool = False,
+                next_norm=None, next_add_ptr: int | None = None) -> bool:
+        if add_ptr is not None:
+            raise ValueError("SandwichBlock: no loop passes in this block form")
+        T, W = ctx.T, x.shape[1]
+        h, y = ctx.buf.h, ctx.buf.y
+        state = list(ctx.cache.state[cache_index]) if cache_index is not None else []
+        self.norm1.forward(x.device_ptr, h.device_ptr, T, W)
+        self.mixer.forward(ctx, h, y, cache_index, state=state)
+        self.norm1b.forward(y.device_ptr, x.device_ptr, T, W, accumulate=True)
+        if self.mlp is not None:
+            self.norm2.forward(x.device_ptr, h.device_ptr, T, W)
+            self.mlp.forward_rows(ctx, h, y)
+            self.norm2b.forward(y.device_ptr, x.device_ptr, T, W, accumulate=True)
+        return False
+
+    @property
+    def weight_bytes(self) -> int:
+        n = self.mixer.weight_bytes + self.norm1.nbytes + self.norm1b.nbytes
+        if self.mlp is not None:
+            n += self.mlp.weight_bytes + self.norm2.nbytes + self.norm2b.nbytes
+        return n
+
+
+__all__ = ["TransformerBlock", "PostNormBlock", "ParallelBlock", "PreNormBlock", "SandwichBlock"]

@@ -109,20 +109,35 @@ class LinearAttentionMixer:
 
 
 class ParallelMixer:
-    def __init__(self, spec: ParallelMixerSpec, layer: int, proj: LinearRows, o_proj: LinearRows, left: PagedAttentionMixer,
-                 right: LinearAttentionMixer):
-        """proj: rows [left q | k | v | right q | k | v | gate]; o_proj: columns [left heads | right heads]; left / right
-        carry the two factors as their `out_mult`."""
+    def __init__(self, spec: ParallelMixerSpec, layer: int, proj: LinearRows, o_proj: "LinearRows | None", left: PagedAttentionMixer,
+                 right, o_left: "LinearRows | None" = None, o_right: "LinearRows | None" = None,
+                 out_weights: "tuple[GPUArray, GPUArray] | None" = None, eps: float = 1e-6):
+        """proj: rows [left q | k | v | right's columns]; join "sum": o_proj with columns [left heads | right heads], left /
+        right carry the two factors as their `out_mult`; join "rms_mean": o_left and o_right, one output projection per side,
+        and out_weights, the weight vectors of the RMS norm over the width that each side's result passes.  `right` is any
+        mixer with a state and an `attend` on a block of columns."""
         self.spec, self.layer, self.proj, self.o_proj, self.left, self.right = spec, layer, proj, o_proj, left, right
+        self.o_left, self.o_right, self.out_weights, self.eps = o_left, o_right, out_weights, float(eps)
         self.proj_cols = left.proj_cols + right.proj_cols
         self.attn_cols = spec.attn_cols
-        if proj.out_features != self.proj_cols or o_proj.in_features != self.attn_cols:
-            raise ValueError(f"layer {layer}: the fused products do not match the two mixers")
+        if spec.join not in ("sum", "rms_mean"):
+            raise ValueError(f"layer {layer}: unknown join {spec.join!r}")
+        if proj.out_features != self.proj_cols:
+            raise ValueError(f"layer {layer}: the fused projection does not match the two mixers")
+        if spec.join == "sum" and (o_proj is None or o_proj.in_features != self.attn_cols):
+            raise ValueError(f"layer {layer}: the fused output projection does not match the two mixers")
+        if spec.join == "rms_mean":
+            if o_left is None or o_right is None or out_weights is None:
+                raise ValueError(f"layer {layer}: the RMS-normed join needs both output projections and both weight vectors")
+            if o_left.in_features != spec.left.attn_cols or o_right.in_features != spec.right.attn_cols:
+                raise ValueError(f"layer {layer}: the output projections do not match the two mixers")
+            if spec.left_scale != spec.right_scale:
+                raise ValueError(f"layer {layer}: the RMS-normed join weighs both sides alike")
         self.queries_per_tile = left.queries_per_tile
 
     @property
     def weight_bytes(self) -> int:
-        return self.proj.nbytes + self.o_proj.nbytes
+        return self.proj.nbytes + sum(o.nbytes for o in (self.o_proj, self.o_left, self.o_right) if o is not None)
 
     def key_slices(self, ctx) -> int:
         return self.left.key_slices(ctx)
@@ -136,6 +151,16 @@ class ParallelMixer:
         self.left.attend(ctx, proj.device_ptr, ld, attn.device_ptr, ldo, cache_index)
         self.right.attend(ctx, proj.device_ptr + 4 * self.left.proj_cols, ld, attn.device_ptr + 4 * self.spec.left.attn_cols,
                           ldo, state)
+        if self.spec.join == "rms_mean":
+            if out_scale is not None:
+                raise ValueError(f"layer {self.layer}: the RMS-normed join stores its result")
+            la, y2 = self.spec.left.attn_cols, ctx.buf.y2
+            Wo = self.o_left.out_features
+            self.o_left.forward(attn.device_ptr, ldo, T, out.device_ptr, Wo)
+            self.o_right.forward(attn.device_ptr + 4 * la, ldo, T, y2.device_ptr, Wo)
+            api.rms_pair_rows_f32(out.device_ptr, self.out_weights[0].device_ptr, y2.device_ptr, self.out_weights[1].device_ptr,
+                                  self.eps, self.spec.left_scale, out.device_ptr, T, Wo, _st())
+            return
         if out_scale is None:
             self.o_proj.forward(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features)
         else:

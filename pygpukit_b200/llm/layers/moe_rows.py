@@ -70,4 +70,71 @@ class GroupedRouterMoE:
         return base, b.moe_parts.device_ptr, inv, b.moe_w.device_ptr, top
 
 
-__all__ = ["GroupedRouterMoE"]
+class BiasedRouterMoE:
+    """Mixture of experts whose router adds a stored correction to the scores when it CHOOSES (the weights are the scores
+    themselves, renormalised or not), whose last `identity` router outputs stand for experts that return their input, and
+    whose shared expert is multiplied by sigmoid of one more projection (a number per token).  The router matrix, float32 in
+    both modes, carries the shared expert's gate as its last row, so that one product gives both.  Experts and row lists as in
+    `GroupedRouterMoE` (rows of experts without matrices sort behind the others and no product touches them; among few rows
+    they are skipped by their matrix number -1).  `forward_rows` leaves the layer's result in `out`:
+
+      pgk_moe_route_biased      scores, choice, weights, row lists
+      pgk_moe_combine_rows_f32  weighted sum of the chosen experts' rows (or the token's own row) + gated shared expert
+    """
+
+    def __init__(self, spec: MoESpec, router: GPUArray, correction: "GPUArray | None", gate_up: "LinearRows | None",
+                 down: "LinearRows | None", shared_gate_up: LinearRows | None = None, shared_down: LinearRows | None = None):
+        """router: [routes (+ 1 with a gated shared expert), W] float32."""
+        self.spec, self.router, self.correction = spec, LinearRows(router), correction
+        self.gate_up, self.down = gate_up, down
+        self.shared_gate_up, self.shared_down = shared_gate_up, shared_down
+        self.z_cols = spec.routes + (1 if spec.shared_gate else 0)
+        if self.router.out_features != self.z_cols:
+            raise ValueError(f"BiasedRouterMoE: the router has {self.router.out_features} rows, the spec needs {self.z_cols}")
+        if spec.experts > 0 and (gate_up is None or gate_up.groups != spec.experts or down.groups != spec.experts):
+            raise ValueError("BiasedRouterMoE: expert stacks do not match the router")
+        if bool(spec.shared_ff) != (shared_gate_up is not None) or (spec.shared_gate and not spec.shared_ff):
+            raise ValueError("BiasedRouterMoE: the shared expert and the spec do not agree")
+
+    @property
+    def weight_bytes(self) -> int:
+        n = self.router.nbytes
+        for m in (self.gate_up, self.down, self.shared_gate_up, self.shared_down):
+            if m is not None:
+                n += m.nbytes
+        return n
+
+    def forward_rows(self, ctx, x: GPUArray, out: GPUArray) -> None:
+        """x [T, W] (the normed rows) -> out [T, W]; out must not be x."""
+        sp, T, b = self.spec, ctx.T, ctx.buf
+        W, top, ff, R = self.router.in_features, sp.top, sp.ff, sp.routes
+        few = T <= LinearRows.FEW
+        self.router.forward(x.device_ptr, W, T, b.moe_z.device_ptr, self.z_cols)          # float32 logits [T, routes (+ 1)]
+        api.moe_route_biased(b.moe_z.device_ptr, self.z_cols, T, R, sp.experts, top,
+                             self.correction.device_ptr if self.correction is not None else None, 1 if sp.renorm else 0,
+                             b.moe_idx.device_ptr, b.moe_mat.device_ptr, b.moe_w.device_ptr,
+                             None if few else b.moe_rank.device_ptr, None if few else b.moe_counts.device_ptr, _st())
+        if few:
+            slot_tok, inv = ctx.slot_rows(top)
+            if sp.experts > 0:
+                self.gate_up.forward_per_row(x.device_ptr, W, T * top, b.moe_act.device_ptr, ff, slot_tok, b.moe_mat.device_ptr)
+                self.down.forward_per_row(b.moe_act.device_ptr, ff, T * top, b.moe_parts.device_ptr, W, None, b.moe_mat.device_ptr)
+        else:
+            api.moe_row_lists(b.moe_counts.device_ptr, b.moe_off.device_ptr, b.moe_idx.device_ptr, b.moe_rank.device_ptr,
+                              b.moe_perm.device_ptr, b.moe_inv.device_ptr, R, T, top, _st())
+            if sp.experts > 0:
+                self.gate_up.forward_grouped(x.device_ptr, W, b.moe_act.device_ptr, ff, b.moe_perm.device_ptr,
+                                             b.moe_off.device_ptr, T)
+                self.down.forward_grouped(b.moe_act.device_ptr, ff, b.moe_parts.device_ptr, W, None, b.moe_off.device_ptr, T)
+            inv = b.moe_inv.device_ptr
+        shared = None
+        if self.shared_gate_up is not None:
+            fs = self.shared_gate_up.out_cols
+            self.shared_gate_up.forward(x.device_ptr, W, T, b.shared_act.device_ptr, fs)
+            self.shared_down.forward(b.shared_act.device_ptr, fs, T, b.y2.device_ptr, W)
+            shared = b.y2.device_ptr
+        api.moe_combine_rows_f32(b.moe_parts.device_ptr, inv, b.moe_mat.device_ptr, b.moe_w.device_ptr, top, x.device_ptr, shared,
+                                 b.moe_z.device_ptr if sp.shared_gate else None, self.z_cols, R, out.device_ptr, T, W, _st())
+
+
+__all__ = ["GroupedRouterMoE", "BiasedRouterMoE"]

@@ -26,14 +26,17 @@ class Norm:
 
 
 class RowNorm:
-    """Norm of float32 rows in the token-major models: "layernorm" (weight, bias; "layernorm_nobias": weight alone) or an RMS norm whose weight enters as
-    (offset + weight) -- offset 1 for weights stored around zero, 0 for plain ones.  `forward` can gather its rows
+    """Norm of float32 rows in the token-major models: "layernorm" (weight, bias; "layernorm_nobias": weight alone), an RMS norm whose weight enters as
+    (offset + weight) -- offset 1 for weights stored around zero, 0 for plain ones -- or "dyt", tanh(alpha x) * weight + bias
+    with a scalar alpha, which computes no mean or variance and has no eps.  `forward` can gather its rows
     (final norm of the wanted rows), add a second summand first and write the sum back (the start of a loop pass), or
     accumulate into the output (a normalised branch added to the residual stream)."""
 
-    def __init__(self, kind: str, weight: GPUArray, bias: GPUArray | None = None, eps: float = 1e-5, offset: float = 0.0):
-        if kind not in ("layernorm", "layernorm_nobias", "rmsnorm"):
+    def __init__(self, kind: str, weight: GPUArray, bias: GPUArray | None = None, eps: float = 1e-5, offset: float = 0.0,
+                 alpha: float = 1.0):
+        if kind not in ("layernorm", "layernorm_nobias", "rmsnorm", "dyt"):
             raise ValueError(f"RowNorm: unknown kind {kind!r}")
+        self.alpha = float(alpha)
         if kind == "layernorm" and bias is None:
             raise ValueError("RowNorm: LayerNorm requires a bias")
         if kind == "layernorm_nobias":
@@ -48,6 +51,13 @@ class RowNorm:
                 add_ptr: int | None = None, sum_out_ptr: int | None = None, accumulate: bool = False) -> None:
         from ..._lib import api
         from ...core.stream import current_stream_handle as _st
+        if self.kind == "dyt":
+            if add_ptr is not None or sum_out_ptr is not None:
+                raise ValueError("RowNorm: a dynamic-tanh row takes no second summand")
+            api.dyt_rows_f32(x_ptr, src_rows, self.alpha, self.weight.device_ptr,
+                             self.bias.device_ptr if self.bias is not None else None, out_ptr, rows, width, 1 if accumulate else 0,
+                             _st())
+            return
         if self.kind == "rmsnorm":
             api.rms_norm_rows_f32(x_ptr, src_rows, add_ptr, sum_out_ptr, self.weight.device_ptr, self.offset, self.eps,
                                   out_ptr, rows, width, 1 if accumulate else 0, _st())

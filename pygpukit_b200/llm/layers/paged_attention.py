@@ -54,10 +54,12 @@ class PagedAttentionMixer:
                  q_norm: "GPUArray | None", k_norm: "GPUArray | None", eps: float, v_role: int = 0, v_lambda: float = 0.0,
                  q_bias: GPUArray | None = None, k_bias: GPUArray | None = None, sinks: GPUArray | None = None,
                  norm_offset: float = 0.0, distance: "tuple[GPUArray, GPUArray] | None" = None,
-                 weight_bias: GPUArray | None = None, out_mult: float = 1.0):
+                 weight_bias: GPUArray | None = None, out_mult: float = 1.0, v_bias: GPUArray | None = None,
+                 head_temp: GPUArray | None = None):
         """qkvg / o_proj None: the mixer is one side of a wider one that owns the products (only `attend` is used).
         distance: the (r1, r2) vectors of the logarithmic distance term; weight_bias: the per-head number of sigmoid weights;
-        out_mult: a constant factor on the heads' outputs."""
+        out_mult: a constant factor on the heads' outputs; q_bias / k_bias / v_bias with `qkv_bias` specs: the projections'
+        biases; head_temp: the per-head factor on the score (it multiplies the query)."""
         self.spec, self.layer = spec, layer
         self.qkvg, self.o_proj = qkvg, o_proj
         self.q_norm, self.k_norm, self.eps = q_norm, k_norm, float(eps)
@@ -82,6 +84,13 @@ class PagedAttentionMixer:
             raise ValueError(f"layer {layer}: kept first positions need a window and no chunks")
         # the preparation launch with rotation / unweighted norm / no norm
         self.rot_prep = s.rot is not None or not s.qk_norm or not s.norm_weight
+        if s.qkv_bias != (q_bias is not None and k_bias is not None and v_bias is not None) and not s.qk_bias:
+            raise ValueError(f"layer {layer}: q / k / v biases and the spec do not agree")
+        if s.head_temp != (head_temp is not None):
+            raise ValueError(f"layer {layer}: the per-head temperature and the spec do not agree")
+        if (s.qkv_bias or s.head_temp) and not self.rot_prep:
+            raise ValueError(f"layer {layer}: q / k / v biases and a per-head temperature ride in the rotary preparation launch")
+        self.v_bias, self.head_temp = v_bias, head_temp
         if self.rot_prep and (s.norm_scope != "head" or s.values != "own" or v_role or s.qk_bias):
             raise ValueError(f"layer {layer}: rotary / unweighted-norm mixers keep their own values, per-head norms and no biases")
         if not self.rot_prep and (q_norm is None or k_norm is None):
@@ -139,13 +148,15 @@ class PagedAttentionMixer:
         ci = self.layer if cache_index is None else cache_index
         kc, vc = cache.k[ci], cache.v[ci]
         if self.rot_prep:
-            api.seq_mixer_prep_rot(proj_ptr, ld, T, s.heads, s.kv_heads, s.dim, s.vdim, 0, self.q_cols, self.q_cols + self.k_cols,
-                                   s.rot.dims if s.rot is not None else 0,
-                                   self.inv_freq.device_ptr if self.inv_freq is not None else None, self.norm_mode,
-                                   self.q_norm.device_ptr if self.q_norm is not None else None,
-                                   self.k_norm.device_ptr if self.k_norm is not None else None, self.eps, kc.device_ptr,
-                                   vc.device_ptr, cache.dtype_code, cache.table_dev.device_ptr, cache.pool.max_pages,
-                                   cache.page_size, ctx.slot_ptr, ctx.pos_ptr, _st())
+            bias = [b.device_ptr if (s.qkv_bias and b is not None) else None for b in (self.q_bias, self.k_bias, self.v_bias)]
+            api.seq_mixer_prep_rot_ex(proj_ptr, ld, T, s.heads, s.kv_heads, s.dim, s.vdim, 0, self.q_cols, self.q_cols + self.k_cols,
+                                      s.rot.dims if s.rot is not None else 0,
+                                      self.inv_freq.device_ptr if self.inv_freq is not None else None, self.norm_mode,
+                                      self.q_norm.device_ptr if self.q_norm is not None else None,
+                                      self.k_norm.device_ptr if self.k_norm is not None else None, self.eps, bias[0], bias[1],
+                                      bias[2], self.head_temp.device_ptr if self.head_temp is not None else None, kc.device_ptr,
+                                      vc.device_ptr, cache.dtype_code, cache.table_dev.device_ptr, cache.pool.max_pages,
+                                      cache.page_size, ctx.slot_ptr, ctx.pos_ptr, _st())
         elif s.norm_scope == "all":
             api.seq_mixer_prep_all(proj_ptr, ld, T, s.heads, s.kv_heads, s.dim, self.q_cols,
                                    self.q_bias.device_ptr if self.q_bias is not None else None,

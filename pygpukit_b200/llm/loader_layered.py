@@ -23,6 +23,14 @@ Rezulorn tensor names: embed, final.norm, head; per layer l<i>.norm1, l<i>.norm2
 l<i>.mlp.{up,down}; "lightning" l<i>.mix.{q,k,v,g,o,norm}; "attention" l<i>.mix.{q,k,v,o,r1,r2}; "parallel"
 l<i>.mix.left.{q,k,v,o,pb} and l<i>.mix.right.{q,k,v,g,o}.  The projections of a mixer are fused row-wise ([q | k | v | g],
 both sides of a parallel mixer in one matrix) and the two output projections of a parallel mixer column-wise.
+
+Sumitar tensor names: embed (also the head), final.norm(.b, .alpha); per layer l<i>.norm1, norm1b, norm2, norm2b, each with .b
+and the scalar .alpha; "parallel" l<i>.mix.left.{q,k,v} with biases .q.b / .k.b / .v.b, .left.temp [heads], .left.o, .left.out,
+l<i>.mix.right.{q,f,v,o}, .right.f.b, .right.lower, .right.norm [vdim], .right.out; "delta" l<i>.mix.{q,k,v} with .conv
+[channels, taps] each, l<i>.mix.{b,a} [heads, width], .A_log, .dt_bias, .norm [vdim], .g, .o; dense feed-forward
+l<i>.mlp.{up,down,act}; experts l<i>.mlp.e<j>.{gate,up,down}, .router [experts + identity, width], .correction,
+.shared.{gate,up,down,sg}.  Both sides' projections of a parallel mixer are one matrix ([left q | k | v | right q | f | v]), a
+delta mixer's are [q | k | v | g | b | a]; the router matrix carries the shared expert's gate row as its last row.
 """
 from __future__ import annotations
 
@@ -35,12 +43,13 @@ from ..core.array import GPUArray
 from ..core.dtypes import bf16_bits_to_f32, f32_to_bf16_bits
 from ..core.factory import from_numpy
 from .config import LayeredConfig, layered_config_from_json
-from .layers.block import ParallelBlock, PostNormBlock, PreNormBlock
-from .layers.dense_rows import GatedDenseRows, SquaredReluRows
+from .layers.block import ParallelBlock, PostNormBlock, PreNormBlock, SandwichBlock
+from .layers.dense_rows import GatedDenseRows, PolyNormRows, SquaredReluRows
+from .layers.gated_recurrent import DeltaRuleMixer, GatedLinearMixer
 from .layers.linear_attention import LinearAttentionMixer, ParallelMixer
 from .layers.latent_attention import LatentAttentionMixer
 from .layers.linear import LinearRows, interleave_gate_up
-from .layers.moe_rows import GroupedRouterMoE
+from .layers.moe_rows import BiasedRouterMoE, GroupedRouterMoE
 from .layers.norm import CausalConvRows, RowNorm
 from .layers.paged_attention import PagedAttentionMixer
 from .layers.token_side import TokenSideInput
@@ -239,8 +248,77 @@ def _build_rezulorn(config: LayeredConfig, t: _Tensors, dtype: str) -> LayeredCa
     return LayeredCausalModel(config, _matrix(t.f32("embed", (V, W)), dtype), blocks, norm("final.norm"), head, dtype)
 
 
+def _build_sumitar(config: LayeredConfig, t: _Tensors, dtype: str) -> LayeredCausalModel:
+    W, V, eps = config.hidden_size, config.vocab_size, config.norm_eps
+
+    def norm(name):
+        return RowNorm("dyt", _vector(t.f32(name, (W,))), _vector(t.f32(name + ".b", (W,))), eps,
+                       alpha=float(t.f32(name + ".alpha").reshape(-1)[0]))
+
+    def per_head(name, heads, vdim):          # a weight vector shared by the heads, laid out per head
+        return _vector(np.tile(t.f32(name, (vdim,)), heads))
+
+    blocks = []
+    for i, L in enumerate(config.layers):
+        p, m = f"l{i}.", L.mixer
+        mp = p + "mix."
+        if m.kind == "parallel":
+            a, r = m.left, m.right
+            lp, rp = mp + "left.", mp + "right."
+            qd, kd, vd = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+            rq, rv = r.heads * r.dim, r.heads * r.vdim
+            fused = np.concatenate([t.f32(lp + "q", (qd, W)), t.f32(lp + "k", (kd, W)), t.f32(lp + "v", (vd, W)),
+                                    t.f32(rp + "q", (rq, W)), t.f32(rp + "f", (rq, W)), t.f32(rp + "v", (rv, W))])
+            left = PagedAttentionMixer(a, i, None, None, None, None, eps, q_bias=_vector(t.f32(lp + "q.b", (qd,))),
+                                       k_bias=_vector(t.f32(lp + "k.b", (kd,))), v_bias=_vector(t.f32(lp + "v.b", (vd,))),
+                                       head_temp=_vector(t.f32(lp + "temp", (a.heads,))))
+            right = GatedLinearMixer(r, i, None, None, _vector(t.f32(rp + "f.b", (rq,))), _vector(t.f32(rp + "lower", (rq,))),
+                                     per_head(rp + "norm", r.heads, r.vdim), eps)
+            mixer = ParallelMixer(m, i, LinearRows(_matrix(fused, dtype)), None, left, right,
+                                  o_left=LinearRows(_matrix(t.f32(lp + "o", (W, a.heads * a.vdim)), dtype)),
+                                  o_right=LinearRows(_matrix(t.f32(rp + "o", (W, rv)), dtype)),
+                                  out_weights=(_vector(t.f32(lp + "out", (W,))), _vector(t.f32(rp + "out", (W,)))), eps=eps)
+        else:
+            qk, vd, H = m.qk_heads * m.dim, m.heads * m.vdim, m.heads
+            fused = np.concatenate([t.f32(mp + "q", (qk, W)), t.f32(mp + "k", (qk, W)), t.f32(mp + "v", (vd, W)),
+                                    t.f32(mp + "g", (vd, W)), t.f32(mp + "b", (H, W)), t.f32(mp + "a", (H, W))])
+            taps = m.conv_taps
+            conv = np.concatenate([t.f32(mp + "q.conv", (qk, taps)), t.f32(mp + "k.conv", (qk, taps)), t.f32(mp + "v.conv", (vd, taps))])
+            mixer = DeltaRuleMixer(m, i, LinearRows(_matrix(fused, dtype)), LinearRows(_matrix(t.f32(mp + "o", (W, vd)), dtype)),
+                                   _vector(conv), _vector(t.f32(mp + "A_log", (H,))), _vector(t.f32(mp + "dt_bias", (H,))),
+                                   per_head(mp + "norm", H, m.vdim), eps)
+        mlp = norm2 = norm2b = None
+        f = L.mlp
+        if f is not None:
+            q = p + "mlp."
+            if f.kind == "dense":
+                mlp = PolyNormRows(f, LinearRows(_matrix(t.f32(q + "up", (f.ff, W)), dtype)),
+                                   LinearRows(_matrix(t.f32(q + "down", (W, f.ff)), dtype)), _vector(t.f32(q + "act", (4,))), eps)
+            else:
+                gu = dn = sgu = sdn = None
+                if f.experts:
+                    gu = LinearRows(_matrix(np.stack([interleave_gate_up(t.f32(f"{q}e{e}.gate", (f.ff, W)), t.f32(f"{q}e{e}.up", (f.ff, W)))
+                                                      for e in range(f.experts)]), dtype), epilogue=1)
+                    dn = LinearRows(_matrix(np.stack([t.f32(f"{q}e{e}.down", (W, f.ff)) for e in range(f.experts)]), dtype))
+                rows = [t.f32(q + "router", (f.routes, W))]
+                if f.shared_ff:
+                    sq = q + "shared."
+                    sgu = LinearRows(_matrix(interleave_gate_up(t.f32(sq + "gate", (f.shared_ff, W)), t.f32(sq + "up", (f.shared_ff, W))),
+                                             dtype), epilogue=1)
+                    sdn = LinearRows(_matrix(t.f32(sq + "down", (W, f.shared_ff)), dtype))
+                    if f.shared_gate:
+                        rows.append(t.f32(sq + "sg", (1, W)))
+                # the router (and the gate row it carries) stays float32 in both modes
+                mlp = BiasedRouterMoE(f, _matrix(np.concatenate(rows), "float32"), _vector(t.f32(q + "correction", (f.routes,))),
+                                      gu, dn, sgu, sdn)
+            norm2, norm2b = norm(p + "norm2"), norm(p + "norm2b")
+        blocks.append(SandwichBlock(norm(p + "norm1"), mixer, norm(p + "norm1b"), norm2, mlp, norm2b))
+    embed = _matrix(t.f32("embed", (V, W)), dtype)
+    return LayeredCausalModel(config, embed, blocks, norm("final.norm"), LinearRows(embed), dtype)
+
+
 # architecture (lower case) -> builder of its blocks from the checkpoint's tensors
-_BUILDERS = {"dolurax": _build_dolurax, "turutar": _build_turutar, "rezulorn": _build_rezulorn}
+_BUILDERS = {"dolurax": _build_dolurax, "turutar": _build_turutar, "rezulorn": _build_rezulorn, "sumitar": _build_sumitar}
 
 
 def load_layered_model(model_path: str, dtype: str = "bfloat16", config: dict | None = None) -> LayeredCausalModel:
