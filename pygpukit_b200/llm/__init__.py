@@ -6,11 +6,12 @@ from .buffers import DecodeBuffers, PrefillBuffers, RowBuffers
 from .config import (GPT2_SPEC, LLAMA_SPEC, MIXTRAL_SPEC, MODEL_SPECS, QWEN2_SPEC, QWEN3_MOE_SPEC, QWEN3_SPEC,
                      GPT2Config, LlamaConfig, ModelSpec, Qwen3Config, TransformerConfig, detect_model_spec,
                      named_config, AttentionMixerSpec, DenseSpec, LatentMixerSpec, LayeredConfig, LayerSpec, LinearMixerSpec, MoESpec,
+                     DeltaMixerSpec, GatedLinearMixerSpec,
                      ParallelMixerSpec, RotarySpec,
                      layered_config_from_json)
 from .decode import (DecodeBatch, DecodeJacobi, DecodeM1, DecodeM1Graph, DecodeSpeculative, DecodeStrategy,
                      RaggedScheduler)
-from .layers import (MLP, Attention, CausalConvRows, LinearAttentionMixer, ParallelMixer, PreNormBlock, SquaredReluRows, GatedDenseRows, GroupedRouterMoE, LatentAttentionMixer, ParallelBlock, RowNorm, TokenSideInput, Linear, LinearBF16, LinearFP8, LinearNVF4, LinearRows, MoELayer, Norm, interleave_gate_up,
+from .layers import (MLP, Attention, BiasedRouterMoE, DeltaRuleMixer, GatedLinearMixer, PolyNormRows, SandwichBlock, CausalConvRows, LinearAttentionMixer, ParallelMixer, PreNormBlock, SquaredReluRows, GatedDenseRows, GroupedRouterMoE, LatentAttentionMixer, ParallelBlock, RowNorm, TokenSideInput, Linear, LinearBF16, LinearFP8, LinearNVF4, LinearRows, MoELayer, Norm, interleave_gate_up,
                      PagedAttentionMixer, PostNormBlock, TransformerBlock,
                      apply_rotary_pos_emb_numpy, precompute_freqs_cis)
 from .models import CausalTransformerModel, GPT2Model, LayeredCausalModel, LlamaModel, QwenModel

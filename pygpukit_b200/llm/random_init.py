@@ -313,6 +313,8 @@ def random_layered_model(config, dtype: str = "bfloat16", seed: int = 1234, std:
         return _random_parallel_model(config, dtype, mat, vec)
     if config.block == "pre_norm":
         return _random_pre_norm_model(config, dtype, mat, vec)
+    if config.block == "sandwich":
+        return _random_sandwich_model(config, dtype, mat, vec)
     blocks, mixing = [], False
     for i, L in enumerate(config.layers):
         m = L.mixer
@@ -426,3 +428,57 @@ def _random_pre_norm_model(config, dtype, mat, vec):
         blocks.append(PreNormBlock(norm(), conv(), mixer, norm2, conv2, mlp, mult))
     head = LinearRows(mat(V, W), epilogue=2, scale=config.logit_scale, cap=0.0)
     return LayeredCausalModel(config, mat(V, W), blocks, norm(), head, dtype)
+
+
+def _random_sandwich_model(config, dtype, mat, vec):
+    """The sandwich-block form of `random_layered_model` (parallel windowed attention + gated linear recurrence, gated delta
+    rule, PolyNorm feed-forward, biased-router experts): random matrices, dynamic-tanh norms at alpha 1 / weight 1 / bias 0,
+    zero projection biases, unit temperatures, forget-gate lower bounds of 0.5, decays and step sizes at fixed values."""
+    from ..core.dtypes import float32
+    from .layers.block import SandwichBlock
+    from .layers.dense_rows import PolyNormRows
+    from .layers.gated_recurrent import DeltaRuleMixer, GatedLinearMixer
+    from .layers.linear import LinearRows
+    from .layers.linear_attention import ParallelMixer
+    from .layers.moe_rows import BiasedRouterMoE
+    from .layers.norm import RowNorm
+    from .layers.paged_attention import PagedAttentionMixer
+    from .models.layered import LayeredCausalModel
+    W, V, eps = config.hidden_size, config.vocab_size, config.norm_eps
+
+    def norm():
+        return RowNorm("dyt", vec(W, 1.0), vec(W, 0.0), eps, alpha=1.0)
+
+    blocks = []
+    for i, L in enumerate(config.layers):
+        m = L.mixer
+        if m.kind == "parallel":
+            a, r = m.left, m.right
+            left = PagedAttentionMixer(a, i, None, None, None, None, eps, q_bias=vec(a.heads * a.dim, 0.0),
+                                       k_bias=vec(a.kv_heads * a.dim, 0.0), v_bias=vec(a.kv_heads * a.vdim, 0.0),
+                                       head_temp=vec(a.heads, 1.0))
+            right = GatedLinearMixer(r, i, None, None, vec(r.heads * r.dim, 0.0), vec(r.heads * r.dim, 0.5),
+                                     vec(r.heads * r.vdim, 1.0), eps)
+            mixer = ParallelMixer(m, i, LinearRows(mat(m.proj_cols, W)), None, left, right,
+                                  o_left=LinearRows(mat(W, a.attn_cols)), o_right=LinearRows(mat(W, r.attn_cols)),
+                                  out_weights=(vec(W, 1.0), vec(W, 1.0)), eps=eps)
+        else:
+            mixer = DeltaRuleMixer(m, i, LinearRows(mat(m.proj_cols, W)), LinearRows(mat(W, m.attn_cols)),
+                                   from_numpy(np.full((m.conv_cols, m.conv_taps), 1.0 / m.conv_taps, np.float32)), vec(m.heads, 0.0),
+                                   vec(m.heads, -2.0), vec(m.heads * m.vdim, 1.0), eps)
+        mlp = norm2 = norm2b = None
+        f = L.mlp
+        if f is not None and f.kind == "dense":
+            mlp = PolyNormRows(f, LinearRows(mat(f.ff, W)), LinearRows(mat(W, f.ff)),
+                               from_numpy(np.asarray([0.5, 0.3, 0.2, 0.0], np.float32)), eps)
+        elif f is not None:
+            sgu = LinearRows(mat(2 * f.shared_ff, W), epilogue=1) if f.shared_ff else None
+            sdn = LinearRows(mat(W, f.shared_ff)) if f.shared_ff else None
+            mlp = BiasedRouterMoE(f, mat(f.routes + (1 if f.shared_gate else 0), W).astype(float32), vec(f.routes, 0.0),
+                                  LinearRows(mat(f.experts, 2 * f.ff, W), epilogue=1) if f.experts else None,
+                                  LinearRows(mat(f.experts, W, f.ff)) if f.experts else None, sgu, sdn)
+        if mlp is not None:
+            norm2, norm2b = norm(), norm()
+        blocks.append(SandwichBlock(norm(), mixer, norm(), norm2, mlp, norm2b))
+    embed = mat(V, W)
+    return LayeredCausalModel(config, embed, blocks, norm(), LinearRows(embed), dtype)

@@ -34,7 +34,7 @@ def softplus(z):
 
 
 def dyt(x, alpha, w, b):
-    return np.tanh(float(alpha) * x) * w + b
+    return np.tanh(float(np.asarray(alpha).reshape(-1)[0]) * x) * w + b
 
 
 def unit_rms(x, eps):
@@ -272,7 +272,7 @@ def random_params(cfg, seed=0):
     def norm(name):
         P[name] = bf(1.0 + 0.1 * rng.standard_normal(W))
         P[name + ".b"] = bf(0.1 * rng.standard_normal(W))
-        P[name + ".alpha"] = bf(np.asarray(rng.uniform(0.4, 1.2)))
+        P[name + ".alpha"] = bf(np.asarray(rng.uniform(0.4, 1.2))).reshape(())
 
     norm("final.norm")
     for i, L in enumerate(cfg["layers"]):
