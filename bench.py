@@ -39,6 +39,10 @@ An option beside the default workload (whose contract is unchanged): prompt and 
     python bench.py --rezulorn [--rezulorn-sizes r-2048,r-4096] [--steps K] [--warmup W]
 The same for the Rezulorn design of the layered family beside a dense Dolurax stack at equal sizes.
 
+    python bench.py --sumitar [--sumitar-sizes s-2048,s-4096] [--steps K] [--warmup W]
+The same for the Sumitar design (windowed attention beside a gated linear recurrence, gated delta rule, PolyNorm feed-forward,
+experts with a choice bias) beside a Rezulorn stack at equal sizes, the closest existing model.
+
     python bench.py --turutar [--turutar-sizes t-2048,t-4096] [--steps K] [--warmup W]
 The same for the Turutar design (latent + windowed attention, gated dense feed-forward, token side inputs, a looped pair of
 layers) next to a Dolurax stack of equal size, the closest existing model: same family, same cache and kernels.
@@ -98,6 +102,11 @@ def parse_args():
                          "convolutions, linear attention with per-sequence state, windowed and sigmoid-weighted attention) "
                          "beside a dense Dolurax stack at equal sizes, one JSON line")
     ap.add_argument("--rezulorn-sizes", default="r-2048,r-4096")
+    ap.add_argument("--sumitar", action="store_true",
+                    help="instead of the default workload: prefill / decode throughput of the Sumitar design (windowed attention "
+                         "beside a gated linear recurrence, gated delta rule, mixture of experts with a choice bias) beside a "
+                         "Rezulorn stack at equal sizes, one JSON line")
+    ap.add_argument("--sumitar-sizes", default="s-2048,s-4096")
     return ap.parse_args()
 
 
@@ -623,6 +632,11 @@ def run_ours(args) -> None:
 
 def main():
     args = parse_args()
+    if args.sumitar:
+        sys.path.insert(0, os.path.join(ROOT, "scripts"))
+        import bench_layered
+        print(json.dumps(bench_layered.main_sumitar(ROOT, args.sumitar_sizes.split(","), args.steps, args.warmup)))
+        return
     if args.rezulorn:
         sys.path.insert(0, os.path.join(ROOT, "scripts"))
         import bench_layered

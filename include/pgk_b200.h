@@ -627,6 +627,13 @@ int pgk_moe_route_biased(const float* logits, int ld, int tokens, int outputs, i
 int pgk_moe_combine_rows_f32(const float* parts, const int32_t* inv, const int32_t* mat, const float* weights, int top,
                              const float* self_rows, const float* shared_rows, const float* gate_rows, int ldg, int gate_off,
                              float* out, int rows, int width, void* stream);
+/* dyt_seam: v = y (mode 0), mult * (y / rms(y) * weight_a + y2 / rms(y2) * weight_b) (mode 1) or the moe_combine_rows sum
+ * (mode 2); x += tanh(alpha1 v) w1 + b1; h = tanh(alpha2 x) w2 + b2 when h is given.  h may be self_rows. */
+int pgk_dyt_seam_f32(int mode, const float* y, const float* y2, const float* weight_a, const float* weight_b, float mult, float eps,
+                     const float* parts, const int32_t* inv, const int32_t* mat, const float* weights, int top,
+                     const float* self_rows, const float* shared_rows, const float* gate_rows, int ldg, int gate_off,
+                     float alpha1, const float* w1, const float* b1, float* x, float alpha2, const float* w2, const float* b2,
+                     float* h, int rows, int width, void* stream);
 int pgk_seq_gated_prep(float* proj, int ld, int tokens, int heads, int dim, int q_off, int f_off, const float* f_bias,
                        const float* lower, void* stream);
 int pgk_seq_delta_prep(float* qk_rows, int ldqk, int q_off, int k_off, float* proj, int ld, int beta_off, int a_off,

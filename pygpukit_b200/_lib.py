@@ -150,6 +150,8 @@ _SIGS = {
     "pgk_polynorm_rows_f32": [vp, i32, vp, f32, i32, i32, vp],
     "pgk_moe_route_biased": [vp, i32, i32, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, vp],
     "pgk_moe_combine_rows_f32": [vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, vp, i32, i32, vp],
+    "pgk_dyt_seam_f32": [i32, vp, vp, vp, vp, f32, f32, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, f32, vp, vp, vp, f32, vp, vp, vp,
+                         i32, i32, vp],
     "pgk_seq_gated_prep": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp],
     "pgk_seq_delta_prep": [vp, i32, i32, i32, vp, i32, i32, i32, vp, vp, i32, i32, i32, i32, f32, vp],
     "pgk_seq_gated_recurrence": [i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, vp, i32, vp, vp, i32,

@@ -9,15 +9,17 @@
 //                      matrices (`mat` = -1 for them)
 //   moe_combine_rows   out = sum_k w[t, k] * (parts row, or the token's own input row for an expert without matrices)
 //                      + sigmoid(gate logit) * shared expert row
+//   dyt_seam           a sublayer's result (plain rows, the two-branch join, or the expert sum) through the norm behind it into
+//                      the residual stream, and the next sublayer's norm of the sum, in one launch
 //   gated_prep         q <- silu(q), f <- low + (1 - low) sigmoid(f + bias) on the fused projection row
 //   delta_prep         q, k heads to unit length (q also times dim^-1/2); beta <- sigmoid(beta); g <- exp(-exp(A_log)
 //                      softplus(a + dt_bias))
 //   gated_recurrence   the state S [dim][vdim] of every (sequence, head) walked token by token:
 //                        gated outer product:  S <- diag(a_t) S + k_t v_t^T,  o_t = S^T q_t     (k_t = 1 - a_t when no keys)
 //                        delta rule:           S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
-//                      A block owns 8 value columns per warp; the rows of S are dealt to the four lanes of a column in groups of
-//                      four, each lane keeps its share in registers, the step's q / k / a rows are staged in shared memory 32
-//                      tokens at a time.  One decoded token is a walk of one.  A sequence whose first position is 0 starts from
+//                      A block owns 4 value columns per warp; the rows of S are dealt to the eight lanes of a column in groups of
+//                      four, each lane keeps its share in registers, the step's q / k / a rows arrive in shared memory 16 tokens
+//                      at a time by asynchronous copies, the next chunk while this one is walked.  One decoded token is a walk of one.  A sequence whose first position is 0 starts from
 //                      zero, whatever its slot held.
 #include "common.cuh"
 #include "../../include/pgk_b200.h"
@@ -158,29 +160,86 @@ struct CombineArgs {
 
 constexpr int CTOP = 64;
 
-__global__ void __launch_bounds__(256) moe_combine_rows_kernel(CombineArgs a) {
-    __shared__ float wk[CTOP];
-    __shared__ long long pk[CTOP];                  // row offset in parts, or -1: the token's own row
-    const int t = blockIdx.x, top = a.top;
-    if (threadIdx.x < top && threadIdx.x < CTOP) {
-        const size_t o = (size_t)t * top + threadIdx.x;
+// the (token, slot) rows of token t staged for the whole block: weights and row offsets in parts (-1: the token's own row)
+__device__ __forceinline__ void combine_stage(const CombineArgs& a, int t, float* wk, long long* pk) {
+    if (threadIdx.x < a.top && threadIdx.x < CTOP) {
+        const size_t o = (size_t)t * a.top + threadIdx.x;
         wk[threadIdx.x] = a.w[o];
         pk[threadIdx.x] = (a.mat && a.mat[o] < 0) ? -1 : (long long)a.inv[o] * a.W;
     }
     __syncthreads();
-    const float sg = a.shared ? (a.gate ? sigmoid_f(a.gate[(size_t)t * a.ldg + a.gate_off]) : 1.f) : 0.f;
-    for (int i = threadIdx.x; i < a.W; i += 256) {
-        float v = 0.f;
-        const int ks = top < CTOP ? top : CTOP;
-        for (int k = 0; k < ks; ++k)
-            v = fmaf(wk[k], pk[k] < 0 ? a.self_rows[(size_t)t * a.W + i] : a.parts[pk[k] + i], v);
-        for (int k = CTOP; k < top; ++k) {
-            const size_t o = (size_t)t * top + k;
-            const bool self = a.mat && a.mat[o] < 0;
-            v = fmaf(a.w[o], self ? a.self_rows[(size_t)t * a.W + i] : a.parts[(size_t)a.inv[o] * a.W + i], v);
+}
+
+__device__ __forceinline__ float combine_value(const CombineArgs& a, int t, int i, const float* wk, const long long* pk, float sg) {
+    float v = 0.f;
+    const int top = a.top, ks = top < CTOP ? top : CTOP;
+    for (int k = 0; k < ks; ++k)
+        v = fmaf(wk[k], pk[k] < 0 ? a.self_rows[(size_t)t * a.W + i] : a.parts[pk[k] + i], v);
+    for (int k = CTOP; k < top; ++k) {
+        const size_t o = (size_t)t * top + k;
+        const bool self = a.mat && a.mat[o] < 0;
+        v = fmaf(a.w[o], self ? a.self_rows[(size_t)t * a.W + i] : a.parts[(size_t)a.inv[o] * a.W + i], v);
+    }
+    if (a.shared) v = fmaf(sg, a.shared[(size_t)t * a.W + i], v);
+    return v;
+}
+
+__device__ __forceinline__ float combine_gate(const CombineArgs& a, int t) {
+    return a.shared ? (a.gate ? sigmoid_f(a.gate[(size_t)t * a.ldg + a.gate_off]) : 1.f) : 0.f;
+}
+
+__global__ void __launch_bounds__(256) moe_combine_rows_kernel(CombineArgs a) {
+    __shared__ float wk[CTOP];
+    __shared__ long long pk[CTOP];
+    const int t = blockIdx.x;
+    combine_stage(a, t, wk, pk);
+    const float sg = combine_gate(a, t);
+    for (int i = threadIdx.x; i < a.W; i += 256) a.out[(size_t)t * a.W + i] = combine_value(a, t, i, wk, pk, sg);
+}
+
+// ---------------------------------------------------------------- a sublayer's result joins the residual stream
+// One launch for the seam behind a sublayer of a block with norms on both sides: the sublayer's result v -- plain rows
+// (mode 0), two branches after an RMS norm each (mode 1), or the weighted sum of expert rows with the gated shared expert
+// (mode 2) -- passes the norm behind the sublayer and joins the residual stream, x += tanh(alpha1 v) w1 + b1, and the norm in
+// front of the next sublayer is taken from the sum at once, h = tanh(alpha2 x) w2 + b2 (h NULL: not wanted).
+struct SeamArgs {
+    int mode;
+    const float* y; const float* y2; const float* wa; const float* wb; float mult, eps;
+    CombineArgs c;
+    float alpha1; const float* w1; const float* b1;
+    float* x;
+    float alpha2; const float* w2; const float* b2; float* h;
+    int W;
+};
+
+__global__ void __launch_bounds__(256) dyt_seam_kernel(SeamArgs a) {
+    __shared__ float red[8];
+    __shared__ float wk[CTOP];
+    __shared__ long long pk[CTOP];
+    const int t = blockIdx.x, W = a.W;
+    const size_t o = (size_t)t * W;
+    float ia = 0.f, ib = 0.f, sg = 0.f;
+    if (a.mode == 1) {
+        float qa = 0.f, qb = 0.f;
+        for (int i = threadIdx.x; i < W; i += 256) {
+            const float u = a.y[o + i], v = a.y2[o + i];
+            qa = fmaf(u, u, qa);
+            qb = fmaf(v, v, qb);
         }
-        if (a.shared) v = fmaf(sg, a.shared[(size_t)t * a.W + i], v);
-        a.out[(size_t)t * a.W + i] = v;
+        ia = a.mult / sqrtf(block_sum(qa, red) / (float)W + a.eps);
+        ib = a.mult / sqrtf(block_sum(qb, red) / (float)W + a.eps);
+    } else if (a.mode == 2) {
+        combine_stage(a.c, t, wk, pk);
+        sg = combine_gate(a.c, t);
+    }
+    for (int i = threadIdx.x; i < W; i += 256) {
+        float v;
+        if (a.mode == 0) v = a.y[o + i];
+        else if (a.mode == 1) v = a.y[o + i] * ia * a.wa[i] + a.y2[o + i] * ib * a.wb[i];
+        else v = combine_value(a.c, t, i, wk, pk, sg);
+        const float xv = a.x[o + i] + fmaf(tanhf(a.alpha1 * v), a.w1[i], a.b1 ? a.b1[i] : 0.f);
+        a.x[o + i] = xv;
+        if (a.h) a.h[o + i] = fmaf(tanhf(a.alpha2 * xv), a.w2[i], a.b2 ? a.b2[i] : 0.f);
     }
 }
 
@@ -233,11 +292,12 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepArgs a) {
 }
 
 // ---------------------------------------------------------------- the recurrence
-constexpr int GR = 4;                 // lanes per value column
+constexpr int GR = 8;                 // lanes per value column
 constexpr int GCW = 32 / GR;          // value columns per warp
-constexpr int GWARPS = 2;             // warps per block
+constexpr int GWARPS = 4;             // warps per block
 constexpr int GCOLS = GWARPS * GCW;   // value columns per block
-constexpr int GTC = 32;               // tokens per staged chunk
+constexpr int GTC = 16;               // tokens per staged chunk
+constexpr int GTHREADS = GWARPS * 32;
 
 struct GatedArgs {
     const float* q; int ldq, q_off;   // head hq at q_off + hq * D of row t; hq = h / (H / G)
@@ -249,59 +309,125 @@ struct GatedArgs {
     float* state;                     // [slots][H][D][Dv]
     const int4* seqs;                 // (first row, rows, slot, first position)
     int H, G, D, Dv;
+    int vec;                          // every row, offset and size a multiple of 16 bytes: chunks arrive by asynchronous copies
 };
 
-// NR: state rows per lane (a multiple of 4); rows 16 j + 4 r + e, j < NR / 4, e < 4 belong to lane group r
+__device__ __forceinline__ void cp_async16(void* smem, const void* g) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* g) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem)), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One stage of the chunk pipeline in shared memory: Q [GTC][Dp], K [GTC][Dp], then the decays [GTC][Dp] (gated outer product)
+// or g, beta and q.k per token [3][GTC] (delta rule), then V [GTC][GCOLS].  Dp = D rounded up to 4 GR; rows D .. Dp - 1 and value
+// columns beyond Dv are zeroed once and never written again.
+template <bool DELTA> __device__ __forceinline__ int stage_floats(int Dp) {
+    return 2 * GTC * Dp + (DELTA ? 3 * GTC : GTC * Dp) + GTC * GCOLS;
+}
+
+// the chunk of nc tokens from row r0 on, by 16-byte asynchronous copies (the caller commits the group)
+template <bool DELTA>
+__device__ __forceinline__ void stage_async(const GatedArgs& a, float* st, int Dp, int r0, int nc, int h, int hq, int col0) {
+    const int D = a.D, D4 = D >> 2, tid = threadIdx.x;
+    float* Qs = st;
+    float* Ks = Qs + GTC * Dp;
+    float* As = Ks + GTC * Dp;
+    float* Vs = As + (DELTA ? 3 * GTC : GTC * Dp);
+    for (int i = tid; i < nc * D4; i += GTHREADS) {
+        const int t = i / D4, d = (i - t * D4) * 4;
+        const size_t row = (size_t)(r0 + t);
+        cp_async16(Qs + t * Dp + d, a.q + row * a.ldq + a.q_off + (size_t)hq * D + d);
+        if (DELTA || a.k) cp_async16(Ks + t * Dp + d, a.k + row * a.ldk + a.k_off + (size_t)hq * D + d);
+        if (!DELTA) cp_async16(As + t * Dp + d, a.a + row * a.lda + a.a_off + (size_t)hq * D + d);
+    }
+    for (int i = tid; i < nc * (GCOLS / 4); i += GTHREADS) {
+        const int t = i / (GCOLS / 4), j = (i - t * (GCOLS / 4)) * 4;
+        if (col0 + j < a.Dv) cp_async16(Vs + t * GCOLS + j, a.v + (size_t)(r0 + t) * a.ldv + a.v_off + (size_t)h * a.Dv + col0 + j);
+    }
+    if (DELTA && tid < nc) {
+        const size_t row = (size_t)(r0 + tid);
+        cp_async4(As + tid, a.a + row * a.lda + a.a_off + h);
+        cp_async4(As + GTC + tid, a.b + row * a.ldb + a.b_off + h);
+    }
+}
+
+// the same chunk by plain loads (rows that are not 16-byte aligned)
+template <bool DELTA>
+__device__ __forceinline__ void stage_plain(const GatedArgs& a, float* st, int Dp, int r0, int nc, int h, int hq, int col0) {
+    const int D = a.D, tid = threadIdx.x;
+    float* Qs = st;
+    float* Ks = Qs + GTC * Dp;
+    float* As = Ks + GTC * Dp;
+    float* Vs = As + (DELTA ? 3 * GTC : GTC * Dp);
+    for (int i = tid; i < nc * D; i += GTHREADS) {
+        const int t = i / D, d = i - t * D;
+        const size_t row = (size_t)(r0 + t);
+        Qs[t * Dp + d] = a.q[row * a.ldq + a.q_off + (size_t)hq * D + d];
+        if (DELTA || a.k) Ks[t * Dp + d] = a.k[row * a.ldk + a.k_off + (size_t)hq * D + d];
+        if (!DELTA) As[t * Dp + d] = a.a[row * a.lda + a.a_off + (size_t)hq * D + d];
+    }
+    for (int i = tid; i < nc * GCOLS; i += GTHREADS) {
+        const int t = i / GCOLS, j = i - t * GCOLS;
+        if (col0 + j < a.Dv) Vs[i] = a.v[(size_t)(r0 + t) * a.ldv + a.v_off + (size_t)h * a.Dv + col0 + j];
+    }
+    if (DELTA && tid < nc) {
+        const size_t row = (size_t)(r0 + tid);
+        As[tid] = a.a[row * a.lda + a.a_off + h];
+        As[GTC + tid] = a.b[row * a.ldb + a.b_off + h];
+    }
+}
+
+// NR: state rows per lane (a multiple of 4); rows 4 GR j + 4 r + e, j < NR / 4, e < 4 belong to lane group r
 template <int NR, bool DELTA>
-__global__ void __launch_bounds__(GWARPS * 32) gated_recurrence_kernel(GatedArgs a) {
+__global__ void __launch_bounds__(GTHREADS) gated_recurrence_kernel(GatedArgs a) {
     extern __shared__ __align__(16) float sm[];
-    const int D = a.D, Dp = (D + 15) & ~15, nj = Dp / 16;
-    float* Qs = sm;                              // [GTC][Dp]
-    float* Ks = Qs + GTC * Dp;                   // [GTC][Dp]
-    float* As = Ks + GTC * Dp;                   // gated outer product: [GTC][Dp]; delta rule: g [GTC], beta [GTC], q.k [GTC]
-    float* Vs = As + (DELTA ? 3 * GTC : GTC * Dp);   // [GTC][GCOLS]
-    float* Os = Vs + GTC * GCOLS;                // [GTC][GCOLS]
+    constexpr int RS = 4 * GR;                   // rows between a lane's groups of four
+    const int D = a.D, Dp = (D + RS - 1) / RS * RS, nj = Dp / RS, SF = stage_floats<DELTA>(Dp);
+    float* Os = sm + 2 * SF;                     // [GTC][GCOLS]
     const int4 sq = a.seqs[blockIdx.x];
     const int row0 = sq.x, n = sq.y, slot = sq.z, pos0 = sq.w;
     const int h = blockIdx.y, hq = h / (a.H / a.G), col0 = blockIdx.z * GCOLS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane / GCW, cc = warp * GCW + (lane % GCW), c = col0 + cc;
-    const bool live = c < a.Dv;
+    const bool live = c < a.Dv, keys = DELTA || a.k != nullptr;
+    for (int i = tid; i < 2 * SF; i += GTHREADS) sm[i] = 0.f;
     float* Sg = a.state + (((size_t)slot * a.H + h) * D) * a.Dv + c;
     float S[NR];
 #pragma unroll
     for (int j = 0; j < NR / 4; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int d = 16 * j + 4 * r + e;
+            const int d = RS * j + 4 * r + e;
             S[4 * j + e] = (pos0 > 0 && live && d < D) ? Sg[(size_t)d * a.Dv] : 0.f;
         }
-    for (int c0 = 0; c0 < n; c0 += GTC) {
-        const int nc = min(GTC, n - c0);
-        __syncthreads();
-        for (int i = tid; i < nc * Dp; i += GWARPS * 32) {
-            const int t = i / Dp, d = i - t * Dp;
-            const size_t row = (size_t)(row0 + c0 + t);
-            const bool in = d < D;
-            Qs[i] = in ? a.q[row * a.ldq + a.q_off + (size_t)hq * D + d] : 0.f;
-            if (DELTA) {
-                Ks[i] = in ? a.k[row * a.ldk + a.k_off + (size_t)hq * D + d] : 0.f;
+    __syncthreads();
+    const int nchunks = (n + GTC - 1) / GTC;
+    if (a.vec) {
+        stage_async<DELTA>(a, sm, Dp, row0, min(GTC, n), h, hq, col0);
+        cp_async_commit();
+    }
+    for (int ci = 0; ci < nchunks; ++ci) {
+        float* st = sm + (ci & 1) * SF;
+        const int c0 = ci * GTC, nc = min(GTC, n - c0);
+        if (a.vec) {
+            if (ci + 1 < nchunks) {              // the next chunk travels while this one is walked
+                stage_async<DELTA>(a, sm + ((ci + 1) & 1) * SF, Dp, row0 + c0 + GTC, min(GTC, n - c0 - GTC), h, hq, col0);
+                cp_async_commit();
+                cp_async_wait<1>();
             } else {
-                const float av = in ? a.a[row * a.lda + a.a_off + (size_t)hq * D + d] : 0.f;
-                As[i] = av;
-                Ks[i] = !in ? 0.f : (a.k ? a.k[row * a.ldk + a.k_off + (size_t)hq * D + d] : 1.f - av);
+                cp_async_wait<0>();
             }
-        }
-        for (int i = tid; i < nc * GCOLS; i += GWARPS * 32) {
-            const int t = i / GCOLS, j = i - t * GCOLS;
-            Vs[i] = col0 + j < a.Dv ? a.v[(size_t)(row0 + c0 + t) * a.ldv + a.v_off + (size_t)h * a.Dv + col0 + j] : 0.f;
-        }
-        if (DELTA && tid < nc) {
-            const size_t row = (size_t)(row0 + c0 + tid);
-            As[tid] = a.a[row * a.lda + a.a_off + h];
-            As[GTC + tid] = a.b[row * a.ldb + a.b_off + h];
+        } else {
+            stage_plain<DELTA>(a, st, Dp, row0 + c0, nc, h, hq, col0);
         }
         __syncthreads();
+        const float* Qs = st;
+        const float* Ks = Qs + GTC * Dp;
+        float* As = st + 2 * GTC * Dp;
+        const float* Vs = As + (DELTA ? 3 * GTC : GTC * Dp);
         if (DELTA) {
             for (int t = warp; t < nc; t += GWARPS) {
                 float s = 0.f;
@@ -311,6 +437,7 @@ __global__ void __launch_bounds__(GWARPS * 32) gated_recurrence_kernel(GatedArgs
             }
             __syncthreads();
         }
+#pragma unroll 2
         for (int t = 0; t < nc; ++t) {
             const float* qr = Qs + t * Dp + 4 * r;
             const float* kr = Ks + t * Dp + 4 * r;
@@ -320,7 +447,7 @@ __global__ void __launch_bounds__(GWARPS * 32) gated_recurrence_kernel(GatedArgs
 #pragma unroll
                 for (int j = 0; j < NR / 4; ++j) {
                     if (j < nj) {
-                        const float4 q4 = *(const float4*)(qr + 16 * j), k4 = *(const float4*)(kr + 16 * j);
+                        const float4 q4 = *(const float4*)(qr + RS * j), k4 = *(const float4*)(kr + RS * j);
                         ks0 = fmaf(k4.x, S[4 * j], ks0); ks1 = fmaf(k4.y, S[4 * j + 1], ks1);
                         ks0 = fmaf(k4.z, S[4 * j + 2], ks0); ks1 = fmaf(k4.w, S[4 * j + 3], ks1);
                         qs0 = fmaf(q4.x, S[4 * j], qs0); qs1 = fmaf(q4.y, S[4 * j + 1], qs1);
@@ -339,7 +466,7 @@ __global__ void __launch_bounds__(GWARPS * 32) gated_recurrence_kernel(GatedArgs
 #pragma unroll
                 for (int j = 0; j < NR / 4; ++j) {
                     if (j < nj) {
-                        const float4 k4 = *(const float4*)(kr + 16 * j);
+                        const float4 k4 = *(const float4*)(kr + RS * j);
                         S[4 * j] = fmaf(g, S[4 * j], k4.x * u);
                         S[4 * j + 1] = fmaf(g, S[4 * j + 1], k4.y * u);
                         S[4 * j + 2] = fmaf(g, S[4 * j + 2], k4.z * u);
@@ -352,8 +479,10 @@ __global__ void __launch_bounds__(GWARPS * 32) gated_recurrence_kernel(GatedArgs
 #pragma unroll
                 for (int j = 0; j < NR / 4; ++j) {
                     if (j < nj) {
-                        const float4 q4 = *(const float4*)(qr + 16 * j), k4 = *(const float4*)(kr + 16 * j);
-                        const float4 a4 = *(const float4*)(ar + 16 * j);
+                        const float4 q4 = *(const float4*)(qr + RS * j), a4 = *(const float4*)(ar + RS * j);
+                        float4 k4;
+                        if (keys) k4 = *(const float4*)(kr + RS * j);
+                        else k4 = make_float4(1.f - a4.x, 1.f - a4.y, 1.f - a4.z, 1.f - a4.w);
                         S[4 * j] = fmaf(a4.x, S[4 * j], k4.x * vc);
                         S[4 * j + 1] = fmaf(a4.y, S[4 * j + 1], k4.y * vc);
                         S[4 * j + 2] = fmaf(a4.z, S[4 * j + 2], k4.z * vc);
@@ -369,7 +498,7 @@ __global__ void __launch_bounds__(GWARPS * 32) gated_recurrence_kernel(GatedArgs
             }
         }
         __syncthreads();
-        for (int i = tid; i < nc * GCOLS; i += GWARPS * 32) {
+        for (int i = tid; i < nc * GCOLS; i += GTHREADS) {
             const int t = i / GCOLS, j = i - t * GCOLS;
             if (col0 + j < a.Dv) a.out[(size_t)(row0 + c0 + t) * a.ldo + (size_t)h * a.Dv + col0 + j] = Os[i];
         }
@@ -379,7 +508,7 @@ __global__ void __launch_bounds__(GWARPS * 32) gated_recurrence_kernel(GatedArgs
         for (int j = 0; j < NR / 4; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int d = 16 * j + 4 * r + e;
+                const int d = RS * j + 4 * r + e;
                 if (d < D) Sg[(size_t)d * a.Dv] = S[4 * j + e];
             }
     }
@@ -392,17 +521,23 @@ int launch_gated(const GatedArgs& a, int n_seqs, size_t smem, cudaStream_t st) {
         PGK_CUDA(cudaFuncSetAttribute(gated_recurrence_kernel<NR, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         configured = true;
     }
-    PGK_CUDA(launch(gated_recurrence_kernel<NR, DELTA>, dim3(n_seqs, a.H, (a.Dv + GCOLS - 1) / GCOLS), dim3(GWARPS * 32), smem, st, a));
+    PGK_CUDA(launch(gated_recurrence_kernel<NR, DELTA>, dim3(n_seqs, a.H, (a.Dv + GCOLS - 1) / GCOLS), dim3(GTHREADS), smem, st, a));
     return 0;
 }
 
+inline bool mult4(long long v) { return (v & 3) == 0; }
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 template <bool DELTA>
-int run_gated(const GatedArgs& a, int n_seqs, cudaStream_t st) {
-    const int Dp = (a.D + 15) & ~15;
-    const size_t smem = sizeof(float) * ((size_t)GTC * Dp * 2 + (DELTA ? 3 * GTC : (size_t)GTC * Dp) + 2 * GTC * GCOLS);
-    if (Dp <= 64) return launch_gated<16, DELTA>(a, n_seqs, smem, st);
-    if (Dp <= 128) return launch_gated<32, DELTA>(a, n_seqs, smem, st);
-    return launch_gated<64, DELTA>(a, n_seqs, smem, st);
+int run_gated(GatedArgs a, int n_seqs, cudaStream_t st) {
+    const int Dp = (a.D + 4 * GR - 1) / (4 * GR) * (4 * GR);
+    const size_t smem = sizeof(float) * (2 * ((size_t)2 * GTC * Dp + (DELTA ? 3 * GTC : (size_t)GTC * Dp) + GTC * GCOLS) + GTC * GCOLS);
+    a.vec = mult4(a.D) && mult4(a.Dv) && mult4(a.ldq) && mult4(a.q_off) && aligned16(a.q) && mult4(a.ldv) && mult4(a.v_off) &&
+            aligned16(a.v) && (!a.k || (mult4(a.ldk) && mult4(a.k_off) && aligned16(a.k))) &&
+            (DELTA || (mult4(a.lda) && mult4(a.a_off) && aligned16(a.a)));
+    if (Dp <= 64) return launch_gated<64 / GR, DELTA>(a, n_seqs, smem, st);
+    if (Dp <= 128) return launch_gated<128 / GR, DELTA>(a, n_seqs, smem, st);
+    return launch_gated<256 / GR, DELTA>(a, n_seqs, smem, st);
 }
 
 }  // namespace
@@ -456,6 +591,24 @@ int pgk_moe_combine_rows_f32(const float* parts, const int32_t* inv, const int32
     if (rows <= 0) return 0;
     CombineArgs a{parts, inv, mat, weights, top, self_rows, shared_rows, gate_rows, ldg, gate_off, out, width};
     PGK_CUDA(launch(moe_combine_rows_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, a));
+    return 0;
+}
+
+int pgk_dyt_seam_f32(int mode, const float* y, const float* y2, const float* weight_a, const float* weight_b, float mult, float eps,
+                     const float* parts, const int32_t* inv, const int32_t* mat, const float* weights, int top,
+                     const float* self_rows, const float* shared_rows, const float* gate_rows, int ldg, int gate_off,
+                     float alpha1, const float* w1, const float* b1, float* x, float alpha2, const float* w2, const float* b2,
+                     float* h, int rows, int width, void* stream) {
+    PGK_REQUIRE(mode >= 0 && mode <= 2 && width > 0 && w1 && x && (!h || w2), "dyt_seam_f32 failed: mode %d, width %d", mode, width);
+    PGK_REQUIRE(mode == 2 || y, "dyt_seam_f32 failed: the sublayer's rows are missing");
+    PGK_REQUIRE(mode != 1 || (y2 && weight_a && weight_b), "dyt_seam_f32 failed: two branches need both rows and both weight vectors");
+    PGK_REQUIRE(mode != 2 || (top >= 0 && (top == 0 || (parts && inv && weights)) && (!mat || self_rows)),
+                "dyt_seam_f32 failed: the expert rows need their index and weights");
+    if (rows <= 0) return 0;
+    SeamArgs a{mode, y, y2, weight_a, weight_b, mult, eps,
+               CombineArgs{parts, inv, mat, weights, top, self_rows, shared_rows, gate_rows, ldg, gate_off, nullptr, width},
+               alpha1, w1, b1, x, alpha2, w2, b2, h, width};
+    PGK_CUDA(launch(dyt_seam_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, a));
     return 0;
 }
 

@@ -432,6 +432,44 @@ int launch_few(const GemmArgs& a, int wdt, int rows_per_block, cudaStream_t st, 
     return launch_few_t<float, EPI, false>(a, rows_per_block, st, batch);
 }
 
+// ---------------------------------------------------------------- many rows, few columns, float32 weights (router logits)
+// A 64 x 64 tile would leave all but one tile column empty and the grid a handful of blocks.  Here a warp owns SKM rows and walks
+// K with a lane per element, SKN columns at a time; the partial sums meet in a warp reduction.  Plain epilogue only.
+constexpr int SKM = 4, SKN = 8, SK_WARPS = 4;
+
+__global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_f32_kernel(GemmArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = (blockIdx.x * SK_WARPS + warp) * SKM;
+    if (m0 >= a.M) return;
+    const float* W = (const float*)a.W;
+    for (int n0 = 0; n0 < a.N; n0 += SKN) {
+        float acc[SKM][SKN];
+#pragma unroll
+        for (int i = 0; i < SKM; ++i)
+#pragma unroll
+            for (int j = 0; j < SKN; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+        for (int k = lane; k < a.K; k += 32) {
+            float x[SKM], w[SKN];
+#pragma unroll
+            for (int i = 0; i < SKM; ++i) x[i] = m0 + i < a.M ? a.A[(size_t)(m0 + i) * a.lda + k] : 0.f;
+#pragma unroll
+            for (int j = 0; j < SKN; ++j) w[j] = n0 + j < a.N ? W[(size_t)(n0 + j) * a.K + k] : 0.f;
+#pragma unroll
+            for (int i = 0; i < SKM; ++i)
+#pragma unroll
+                for (int j = 0; j < SKN; ++j) acc[i][j] = fmaf(x[i], w[j], acc[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < SKM; ++i)
+#pragma unroll
+            for (int j = 0; j < SKN; ++j) {
+                const float v = warp_sum(acc[i][j]);
+                if (lane == 0 && m0 + i < a.M && n0 + j < a.N) a.C[(size_t)(m0 + i) * a.ldc + n0 + j] = v;
+            }
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -448,6 +486,10 @@ int pgk_gemm_rows_f32(const float* A, int lda, const int32_t* a_rows, const void
     if (rows <= 0 || G <= 0) return 0;
     GemmArgs a{A, a_rows, W, C, group_off, nullptr, w_group_stride, lda, ldc, M, N, K, scale, cap, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
     cudaStream_t st = (cudaStream_t)stream;
+    if (wdt == 0 && epilogue == 0 && !group_off && !a_rows && N <= 64) {        // router logits: few columns, float32 weights
+        PGK_CUDA(launch(gemm_skinny_f32_kernel, dim3((M + SK_WARPS * SKM - 1) / (SK_WARPS * SKM)), dim3(SK_WARPS * 32), 0, st, a));
+        return 0;
+    }
     if (epilogue == 0) return launch_many<0>(a, wdt, G, rows, st);
     if (epilogue == 1) return launch_many<1>(a, wdt, G, rows, st);
     return launch_many<2>(a, wdt, G, rows, st);

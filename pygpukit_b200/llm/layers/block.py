@@ -210,16 +210,22 @@ class PreNormBlock:
 
 class SandwichBlock:
     """Block of the token-major models with a norm before AND after each sublayer: x += norm1b(mixer(norm1(x))), then
-    x += norm2b(ff(norm2(x))).  The norms are `RowNorm`s of any kind; the one behind a sublayer adds its result to the residual
-    stream in its own launch.  The feed-forward is any layer with `forward_rows(ctx, rows, out)`.  Per-sequence state of the
-    block in the cache manager: whatever the mixer keeps."""
+    x += norm2b(ff(norm2(x))).  The norms are `RowNorm`s of any kind.  With dynamic-tanh norms the seam behind a sublayer is
+    ONE launch (pgk_dyt_seam_f32): the sublayer's last step -- the join of a parallel mixer's two RMS-normed sides, or the
+    weighted sum of the chosen experts with the gated shared expert -- the norm behind it, the residual add, and the norm in
+    front of the next sublayer (the feed-forward's, or the next block's first one).  Other norms take a launch each.  The
+    feed-forward is any layer with `forward_rows(ctx, rows, out)`.  Per-sequence state of the block in the cache manager:
+    whatever the mixer keeps."""
 
     def __init__(self, norm1, mixer, norm1b, norm2=None, mlp=None, norm2b=None):
         self.norm1, self.mixer, self.norm1b, self.norm2, self.mlp, self.norm2b = norm1, mixer, norm1b, norm2, mlp, norm2b
         if (mlp is None) != (norm2 is None) or (mlp is None) != (norm2b is None):
             raise ValueError("SandwichBlock: a feed-forward comes with both of its norms")
 
-    norm = None                          # the block's norms are not fused with the block before
+    @property
+    def norm(self):
+        """the norm in front of the block: the block before may write its rows (dynamic-tanh norms only)"""
+        return self.norm1 if self.norm1.kind == "dyt" else None
 
     @property
     def state_shapes(self) -> tuple:
@@ -227,19 +233,58 @@ class SandwichBlock:
 
     def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None, normed: bool = False,
                 next_norm=None, next_add_ptr: int | None = None) -> bool:
+        """normed: ctx.buf.h already holds norm1(x) (the block before wrote it).  next_norm: the first norm of the block that
+        runs next; returns True when this block has written that block's normed rows."""
         if add_ptr is not None:
             raise ValueError("SandwichBlock: no loop passes in this block form")
         T, W = ctx.T, x.shape[1]
         h, y = ctx.buf.h, ctx.buf.y
         state = list(ctx.cache.state[cache_index]) if cache_index is not None else []
-        self.norm1.forward(x.device_ptr, h.device_ptr, T, W)
-        self.mixer.forward(ctx, h, y, cache_index, state=state)
-        self.norm1b.forward(y.device_ptr, x.device_ptr, T, W, accumulate=True)
-        if self.mlp is not None:
+        if next_add_ptr is not None:
+            next_norm = None
+        if not normed:
+            self.norm1.forward(x.device_ptr, h.device_ptr, T, W)
+        if hasattr(self.mixer, "forward_pending"):
+            pend = self.mixer.forward_pending(ctx, h, y, cache_index, state=state)
+        else:
+            self.mixer.forward(ctx, h, y, cache_index, state=state)
+            pend = {"mode": "rows", "y": y.device_ptr}
+        wrote = self._seam(ctx, pend, self.norm1b, x, self.norm2 if self.mlp is not None else next_norm)
+        if self.mlp is None:
+            return wrote
+        if not wrote:
             self.norm2.forward(x.device_ptr, h.device_ptr, T, W)
+        if hasattr(self.mlp, "forward_pending"):
+            pend = self.mlp.forward_pending(ctx, h, y)
+        else:
             self.mlp.forward_rows(ctx, h, y)
-            self.norm2b.forward(y.device_ptr, x.device_ptr, T, W, accumulate=True)
-        return False
+            pend = {"mode": "rows", "y": y.device_ptr}
+        return self._seam(ctx, pend, self.norm2b, x, next_norm)
+
+    @staticmethod
+    def _seam(ctx, p: dict, post, x: GPUArray, nxt) -> bool:
+        """x += post(the pending result); h = nxt(x) when the launch can take it along (returns whether it did)."""
+        from ..._lib import api
+        from ...core.stream import current_stream_handle as _st
+        T, W = ctx.T, x.shape[1]
+        h, y = ctx.buf.h, ctx.buf.y
+        if post.kind != "dyt":                       # finish the pending step into y, then the norm's own launch
+            if p["mode"] == "pair":
+                api.rms_pair_rows_f32(p["y"], p["wa"], p["y2"], p["wb"], p["eps"], p["mult"], y.device_ptr, T, W, _st())
+            elif p["mode"] == "experts":
+                api.moe_combine_rows_f32(p["parts"], p["inv"], p["mat"], p["w"], p["top"], p["self_rows"], p["shared"], p["gate"],
+                                         p["ldg"], p["gate_off"], y.device_ptr, T, W, _st())
+            post.forward(y.device_ptr if p["mode"] != "rows" else p["y"], x.device_ptr, T, W, accumulate=True)
+            return False
+        take = nxt is not None and nxt.kind == "dyt"
+        mode = {"rows": 0, "pair": 1, "experts": 2}[p["mode"]]
+        api.dyt_seam_f32(mode, p.get("y"), p.get("y2"), p.get("wa"), p.get("wb"), p.get("mult", 1.0), p.get("eps", 0.0),
+                         p.get("parts"), p.get("inv"), p.get("mat"), p.get("w"), p.get("top", 0), p.get("self_rows"), p.get("shared"),
+                         p.get("gate"), p.get("ldg", 0), p.get("gate_off", 0), post.alpha, post.weight.device_ptr,
+                         post.bias.device_ptr if post.bias is not None else None, x.device_ptr,
+                         nxt.alpha if take else 1.0, nxt.weight.device_ptr if take else None,
+                         nxt.bias.device_ptr if take and nxt.bias is not None else None, h.device_ptr if take else None, T, W, _st())
+        return take
 
     @property
     def weight_bytes(self) -> int:

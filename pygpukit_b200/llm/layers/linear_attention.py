@@ -142,8 +142,22 @@ class ParallelMixer:
     def key_slices(self, ctx) -> int:
         return self.left.key_slices(ctx)
 
-    def forward(self, ctx, x: GPUArray, out: GPUArray, cache_index: int | None = None, out_scale: int | None = None,
-                state=None) -> None:
+    def forward_pending(self, ctx, x: GPUArray, out: GPUArray, cache_index: int | None = None, state=None) -> dict:
+        """`forward` without its last launch, for a block that folds the join into its own seam launch: the description of
+        what is still to be done ("pair": the two sides' projected rows and the weights of their RMS norms; "rows": nothing)."""
+        if self.spec.join != "rms_mean":
+            self.forward(ctx, x, out, cache_index, state=state)
+            return {"mode": "rows", "y": out.device_ptr}
+        T = ctx.T
+        attn, y2 = ctx.buf.attn, ctx.buf.y2
+        ldo, la, Wo = self.attn_cols, self.spec.left.attn_cols, self.o_left.out_features
+        self._attend(ctx, x, cache_index, state)
+        self.o_left.forward(attn.device_ptr, ldo, T, out.device_ptr, Wo)
+        self.o_right.forward(attn.device_ptr + 4 * la, ldo, T, y2.device_ptr, Wo)
+        return {"mode": "pair", "y": out.device_ptr, "y2": y2.device_ptr, "wa": self.out_weights[0].device_ptr,
+                "wb": self.out_weights[1].device_ptr, "mult": self.spec.left_scale, "eps": self.eps}
+
+    def _attend(self, ctx, x: GPUArray, cache_index, state) -> None:
         T, W = ctx.T, self.proj.in_features
         proj, attn = ctx.buf.proj, ctx.buf.attn
         ld, ldo = self.proj_cols, self.attn_cols
@@ -151,16 +165,19 @@ class ParallelMixer:
         self.left.attend(ctx, proj.device_ptr, ld, attn.device_ptr, ldo, cache_index)
         self.right.attend(ctx, proj.device_ptr + 4 * self.left.proj_cols, ld, attn.device_ptr + 4 * self.spec.left.attn_cols,
                           ldo, state)
+
+    def forward(self, ctx, x: GPUArray, out: GPUArray, cache_index: int | None = None, out_scale: int | None = None,
+                state=None) -> None:
+        T = ctx.T
+        attn, ldo = ctx.buf.attn, self.attn_cols
         if self.spec.join == "rms_mean":
             if out_scale is not None:
                 raise ValueError(f"layer {self.layer}: the RMS-normed join stores its result")
-            la, y2 = self.spec.left.attn_cols, ctx.buf.y2
-            Wo = self.o_left.out_features
-            self.o_left.forward(attn.device_ptr, ldo, T, out.device_ptr, Wo)
-            self.o_right.forward(attn.device_ptr + 4 * la, ldo, T, y2.device_ptr, Wo)
-            api.rms_pair_rows_f32(out.device_ptr, self.out_weights[0].device_ptr, y2.device_ptr, self.out_weights[1].device_ptr,
-                                  self.eps, self.spec.left_scale, out.device_ptr, T, Wo, _st())
+            p = self.forward_pending(ctx, x, out, cache_index, state)
+            api.rms_pair_rows_f32(p["y"], p["wa"], p["y2"], p["wb"], p["eps"], p["mult"], out.device_ptr, T,
+                                  self.o_left.out_features, _st())
             return
+        self._attend(ctx, x, cache_index, state)
         if out_scale is None:
             self.o_proj.forward(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features)
         else:

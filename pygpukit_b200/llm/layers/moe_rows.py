@@ -106,6 +106,13 @@ class BiasedRouterMoE:
 
     def forward_rows(self, ctx, x: GPUArray, out: GPUArray) -> None:
         """x [T, W] (the normed rows) -> out [T, W]; out must not be x."""
+        p = self.forward_pending(ctx, x)
+        api.moe_combine_rows_f32(p["parts"], p["inv"], p["mat"], p["w"], p["top"], p["self_rows"], p["shared"], p["gate"], p["ldg"],
+                                 p["gate_off"], out.device_ptr, ctx.T, self.router.in_features, _st())
+
+    def forward_pending(self, ctx, x: GPUArray, out: "GPUArray | None" = None) -> dict:
+        """Everything but the weighted sum, for a block that folds the sum into its own seam launch: the description of the
+        rows to be summed ("experts")."""
         sp, T, b = self.spec, ctx.T, ctx.buf
         W, top, ff, R = self.router.in_features, sp.top, sp.ff, sp.routes
         few = T <= LinearRows.FEW
@@ -133,8 +140,9 @@ class BiasedRouterMoE:
             self.shared_gate_up.forward(x.device_ptr, W, T, b.shared_act.device_ptr, fs)
             self.shared_down.forward(b.shared_act.device_ptr, fs, T, b.y2.device_ptr, W)
             shared = b.y2.device_ptr
-        api.moe_combine_rows_f32(b.moe_parts.device_ptr, inv, b.moe_mat.device_ptr, b.moe_w.device_ptr, top, x.device_ptr, shared,
-                                 b.moe_z.device_ptr if sp.shared_gate else None, self.z_cols, R, out.device_ptr, T, W, _st())
+        return {"mode": "experts", "parts": b.moe_parts.device_ptr, "inv": inv, "mat": b.moe_mat.device_ptr, "w": b.moe_w.device_ptr,
+                "top": top, "self_rows": x.device_ptr, "shared": shared, "gate": b.moe_z.device_ptr if sp.shared_gate else None,
+                "ldg": self.z_cols, "gate_off": R}
 
 
 __all__ = ["GroupedRouterMoE", "BiasedRouterMoE"]

@@ -50,6 +50,17 @@ REZULORN_SIZES = {
 }
 
 
+# Sumitar: sandwich blocks with dynamic-tanh norms; a parallel layer (windowed rotary attention beside a gated linear
+# recurrence, each side RMS-normed over the width) with a PolyNorm feed-forward, and a gated-delta-rule layer with a mixture of
+# experts (choice bias, experts without matrices, gated shared expert)
+SUMITAR_SIZES = {
+    "s-2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, rot=64, lin_heads=16, lin_dim=128, lin_vdim=128,
+                   qk_heads=4, taps=4, ff=8192, experts=16, identity=2, top=4, eff=2048, shared_ff=2048, vocab=32768),
+    "s-4096": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, rot=64, lin_heads=32, lin_dim=128, lin_vdim=128,
+                   qk_heads=8, taps=4, ff=12288, experts=16, identity=2, top=4, eff=3072, shared_ff=3072, vocab=32768),
+}
+
+
 def peaks(root: str) -> tuple[float, float, str]:
     p = os.path.join(root, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -159,6 +170,69 @@ def twin_bytes_flops(s: dict, T: int, B: int, ctx: int) -> tuple[float, float]:
     seen_avg = min(T, s["window"]) / 2
     fl = n * (2 * T * layer_w + 2 * T * H * seen_avg * 2 * D) + 2 * s["vocab"] * W
     return float(dec), float(fl)
+
+
+def sumitar_config(s: dict):
+    from pygpukit_b200.llm.config import layered_config_from_json
+    H, G, D, Hl, Dl, Dvl = s["heads"], s["kv_heads"], s["dim"], s["lin_heads"], s["lin_dim"], s["lin_vdim"]
+    left = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": s["window"]},
+            "rot": {"dims": s["rot"], "base": 10000.0}}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"]},
+           "shared": {"ff": s["shared_ff"]}}
+    layers = [{"type": "parallel", "mlp": {"kind": "dense", "ff": s["ff"]},
+               "mixer": {"left": left, "right": {"heads": Hl, "dim": Dl, "vdim": Dvl}}},
+              {"type": "delta", "mlp": moe, "mixer": {"heads": Hl, "kv_heads": s["qk_heads"], "dim": Dl, "vdim": Dvl, "conv": s["taps"]}}]
+    return layered_config_from_json({"architecture": "Sumitar", "layers": layers, "norm": {"eps": 1e-6}, "vocab": s["vocab"],
+                                     "width": s["width"]})
+
+
+def sumitar_twin_config(s: dict):
+    """The closest existing model at equal size: a Rezulorn stack of a parallel layer (rotary attention beside rotary retention
+    with per-sequence state) and a lightning layer (decayed linear attention, state only), the same heads, squared-ReLU
+    feed-forward of the dense size in both."""
+    from pygpukit_b200.llm.config import layered_config_from_json
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    H, G, D, Hl, Dl, Dvl = s["heads"], s["kv_heads"], s["dim"], s["lin_heads"], s["lin_dim"], s["lin_vdim"]
+    decay = [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, Hl - 1)) for h in range(Hl)]
+    left = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "rot": {"dims": D, "base": 10000.0}}
+    right = {"heads": Hl, "dim": Dl, "vdim": Dvl, "decay": decay, "rot": {"dims": Dl, "base": 100000.0}}
+    layers = [{"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 0.75}},
+              {"type": "lightning", "mlp": mlp, "mixer": {"heads": Hl, "dim": Dl, "vdim": Dvl, "decay": decay}}]
+    return layered_config_from_json({"architecture": "Rezulorn", "layers": layers, "canon": {"taps": s["taps"]}, "norm": {"eps": 1e-6},
+                                     "residual_mult": 0.5, "logit_scale": 1.0, "vocab": s["vocab"], "width": s["width"]})
+
+
+def sumitar_bytes_flops(s: dict, T: int, B: int, ctx: int) -> tuple[float, float]:
+    """(bytes a decode step of B tokens touches, FLOPs of a T-token prefill; the recurrences counted in their recurrent form)"""
+    W, H, G, D = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    Hl, Dl, Dvl, Gq = s["lin_heads"], s["lin_dim"], s["lin_vdim"], s["qk_heads"]
+    par_w = (H * D + 2 * G * D + 2 * Hl * Dl + Hl * Dvl) * W + W * H * D + W * Hl * Dvl
+    delta_w = (2 * Gq * Dl + 2 * Hl * Dvl + 2 * Hl) * W + W * Hl * Dvl
+    dense_w = 2 * s["ff"] * W
+    routes = s["experts"] + s["identity"]
+    moe_fix = (routes + 1) * W * 2 + 3 * s["shared_ff"] * W              # the router is float32: twice the bytes per element
+    act = min(s["experts"], B * s["top"])
+    state = 2 * 4 * Hl * Dl * Dvl                                         # float32, read and written, per recurrent mixer
+    seen = min(ctx, s["window"])
+    dec = 2 * (par_w + delta_w + dense_w + moe_fix + act * 3 * s["eff"] * W) + B * (2 * 2 * G * D * seen + 2 * state) + 2 * s["vocab"] * W
+    win = s["window"]
+    seen_avg = min(T, win) / 2 if T <= win else win * (1 - win / (2 * T))
+    share = s["experts"] / routes                                         # chosen experts that have matrices, on average
+    per_tok = par_w + delta_w + dense_w + routes * W + 3 * s["shared_ff"] * W + s["top"] * share * 3 * s["eff"] * W
+    attn_fl = 2 * T * H * seen_avg * 2 * D + 2 * T * Hl * 3 * Dl * Dvl + 2 * T * Hl * 4 * Dl * Dvl
+    return float(dec), float(2 * T * per_tok + attn_fl + 2 * s["vocab"] * W)
+
+
+def sumitar_twin_bytes_flops(s: dict, T: int, B: int, ctx: int) -> tuple[float, float]:
+    W, H, G, D = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    Hl, Dl, Dvl = s["lin_heads"], s["lin_dim"], s["lin_vdim"]
+    att_w = (H * D + 2 * G * D) * W + W * H * D
+    lin_w = (2 * Hl * Dl + 2 * Hl * Dvl) * W + W * Hl * Dvl
+    weights = att_w + 2 * lin_w + 2 * 2 * s["ff"] * W
+    state = 2 * 4 * Hl * Dl * Dvl
+    dec = 2 * weights + B * (2 * 2 * G * D * ctx + 2 * state) + 2 * s["vocab"] * W
+    attn_fl = 2 * T * H * (T / 2) * 2 * D + 2 * 2 * T * Hl * 4 * Dl * Dvl
+    return float(dec), float(2 * T * weights + attn_fl + 2 * s["vocab"] * W)
 
 
 def _timed(fn, iters: int, warm: int) -> float:
@@ -329,6 +403,27 @@ def main_rezulorn(root: str, sizes: list[str], steps: int, warm: int, prompt: in
         twin = dict(s, times=1.5)
         entry["dolurax_dense_twin"] = run_layered(rezulorn_twin_config(s), lambda T, B, ctx: twin_bytes_flops(twin, T, B, ctx), s["vocab"],
                                                   prompt, (1, 8), steps, max(3, warm), hbm, tflops)
+        api.device_sync()
+        res["sizes"][name] = entry
+    return res
+
+
+def main_sumitar(root: str, sizes: list[str], steps: int, warm: int, prompt: int = 2000) -> dict:
+    """Sumitar beside a Rezulorn stack of the same family at equal size (a parallel layer and a state-only layer): prefill of
+    `prompt` tokens, decode of 1 and 8 requests at that context."""
+    from pygpukit_b200._lib import api
+    hbm, tflops, src = peaks(root)
+    res = {"metric": "sumitar_prefill_decode_tokens_per_s", "data": "synthetic",
+           "dtype": "bf16 matrices and cache, f32 residual / norms / scores / router / recurrent state",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "prompt": prompt, "steps": steps, "warmup": warm, "sizes": {}}
+    for name in sizes:
+        s = SUMITAR_SIZES[name]
+        entry = {"shape": dict(s)}
+        entry["sumitar"] = run_layered(sumitar_config(s), lambda T, B, ctx: sumitar_bytes_flops(s, T, B, ctx), s["vocab"], prompt,
+                                       (1, 8), steps, max(3, warm), hbm, tflops)
+        api.device_sync()
+        entry["rezulorn_twin"] = run_layered(sumitar_twin_config(s), lambda T, B, ctx: sumitar_twin_bytes_flops(s, T, B, ctx), s["vocab"],
+                                             prompt, (1, 8), steps, max(3, warm), hbm, tflops)
         api.device_sync()
         res["sizes"][name] = entry
     return res
