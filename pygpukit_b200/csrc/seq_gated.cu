@@ -17,7 +17,7 @@
 //   gated_recurrence   the state S [dim][vdim] of every (sequence, head) walked token by token:
 //                        gated outer product:  S <- diag(a_t) S + k_t v_t^T,  o_t = S^T q_t     (k_t = 1 - a_t when no keys)
 //                        delta rule:           S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
-//                      A block owns 4 value columns per warp; the rows of S are dealt to the eight lanes of a column in groups of
+//                      A block owns 2 value columns per warp; the rows of S are dealt to the sixteen lanes of a column in groups of
 //                      four, each lane keeps its share in registers, the step's q / k / a rows arrive in shared memory 16 tokens
 //                      at a time by asynchronous copies, the next chunk while this one is walked.  One decoded token is a walk of one.  A sequence whose first position is 0 starts from
 //                      zero, whatever its slot held.
@@ -292,9 +292,9 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepArgs a) {
 }
 
 // ---------------------------------------------------------------- the recurrence
-constexpr int GR = 8;                 // lanes per value column
+constexpr int GR = 16;                // lanes per value column
 constexpr int GCW = 32 / GR;          // value columns per warp
-constexpr int GWARPS = 4;             // warps per block
+constexpr int GWARPS = 8;             // warps per block
 constexpr int GCOLS = GWARPS * GCW;   // value columns per block
 constexpr int GTC = 16;               // tokens per staged chunk
 constexpr int GTHREADS = GWARPS * 32;
