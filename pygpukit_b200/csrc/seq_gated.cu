@@ -1,6 +1,6 @@
 // seq_gated.cu -- the token-major models' pieces with DATA-DEPENDENT gates, all in float32:
 //
-//   dyt_rows           tanh(alpha x) * w + b on rows (a norm that computes no mean or variance); rows may be gathered, and the
+//   dyt_rows           tanh(alpha x) * w + b on rows (a pointwise squashing in the place of a norm: no statistic of the row); rows may be gathered, and the
 //                      result may be added to the output (a normalised branch joining the residual stream)
 //   rms_pair_rows      mult * (a / rms(a) * wa + b / rms(b) * wb): two branches joined after an RMS norm each
 //   polynorm_rows      c0 z / rms(z) + c1 z^2 / rms(z^2) + c2 z^3 / rms(z^3) + c3, in place on the rows of a feed-forward
@@ -232,7 +232,8 @@ __global__ void __launch_bounds__(256) dyt_seam_kernel(SeamArgs a) {
         combine_stage(a.c, t, wk, pk);
         sg = combine_gate(a.c, t);
     }
-    for (int i = threadIdx.x; i < W; i += 256) {
+    // few rows: gridDim.y blocks share a row's columns (each forms the row's two sums itself in mode 1)
+    for (int i = blockIdx.y * 256 + threadIdx.x; i < W; i += gridDim.y * 256) {
         float v;
         if (a.mode == 0) v = a.y[o + i];
         else if (a.mode == 1) v = a.y[o + i] * ia * a.wa[i] + a.y2[o + i] * ib * a.wb[i];
@@ -608,7 +609,8 @@ int pgk_dyt_seam_f32(int mode, const float* y, const float* y2, const float* wei
     SeamArgs a{mode, y, y2, weight_a, weight_b, mult, eps,
                CombineArgs{parts, inv, mat, weights, top, self_rows, shared_rows, gate_rows, ldg, gate_off, nullptr, width},
                alpha1, w1, b1, x, alpha2, w2, b2, h, width};
-    PGK_CUDA(launch(dyt_seam_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, a));
+    const int by = rows <= 32 ? (width + 511) / 512 < 8 ? (width + 511) / 512 : 8 : 1;
+    PGK_CUDA(launch(dyt_seam_kernel, dim3(rows, by), dim3(256), 0, (cudaStream_t)stream, a));
     return 0;
 }
 

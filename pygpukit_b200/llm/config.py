@@ -357,7 +357,7 @@ class LinearMixerSpec:
 
 @dataclass(frozen=True)
 class GatedLinearMixerSpec:
-    """Linear attention whose forget gate also decides what is written, with a float32 state per sequence:
+    """A linear recurrence that writes with the complement of its forget gate, with a float32 state per sequence:
     S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t, per head; f_t = low + (1 - low) sigmoid(W_f h + b_f) per head
     and channel with a learned lower bound, q = silu(W_q h); there is no key.  Every head's output is divided by its root
     mean square and multiplied by a weight vector shared by the heads."""

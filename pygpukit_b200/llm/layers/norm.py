@@ -28,7 +28,7 @@ class Norm:
 class RowNorm:
     """Norm of float32 rows in the token-major models: "layernorm" (weight, bias; "layernorm_nobias": weight alone), an RMS norm whose weight enters as
     (offset + weight) -- offset 1 for weights stored around zero, 0 for plain ones -- or "dyt", tanh(alpha x) * weight + bias
-    with a scalar alpha, which computes no mean or variance and has no eps.  `forward` can gather its rows
+    with a scalar alpha, a pointwise squashing that takes no statistic of the row and has no eps.  `forward` can gather its rows
     (final norm of the wanted rows), add a second summand first and write the sum back (the start of a loop pass), or
     accumulate into the output (a normalised branch added to the residual stream)."""
 

@@ -3,7 +3,7 @@ no code shared with the package.  Notation: T tokens, W width, H heads, G key/va
 value size.
 
     layer        x += N1b(mixer(N1(x)));  x += N2b(ff(N2(x)))          N = dyt
-    dyt(x)       tanh(alpha x) * w + b                                  (alpha a scalar; no mean, no variance)
+    dyt(x)       tanh(alpha x) * w + b                                  (alpha a scalar; pointwise)
     parallel     ( rms(left) * w_l + rms(right) * w_r ) / 2            rms over the width, both sides read the same input
       left       q, k, v = W h + bias;  q, k rotated (half layout, first `dims`, angle p * base^(-2i/dims));
                  s_ij = scale temp_h q_i.k_j;  j visible when 0 <= i - j < window;  softmax;  W_o
